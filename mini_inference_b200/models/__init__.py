@@ -1,0 +1,2 @@
+"""Built-in architectures; importing this package registers them."""
+from . import qwen3  # noqa: F401

@@ -1,0 +1,55 @@
+"""Grouped-query attention over the paged cache (engine/core/model_runner.py:137-196).
+
+q, k, v come from one product on the concatenated weight [(H+2KV)*D, hidden]
+(engine/core/fused_linear.py:167-169).  One kernel then applies the per-head q/k RMSNorm
+(weights shared by all heads, :148-150), rotates q and k (:151-152) and writes k and v into
+the step's pages BEFORE attention runs, so a portion attends to itself through the cache
+(:156).  Attention reads the pages in place for prompt portions and decoded tokens alike."""
+from __future__ import annotations
+
+import torch
+
+from .base import KVCacheNeed, Part, WeightSpec, register_mixer
+
+
+@register_mixer("gqa_attention")
+class GQAAttention(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = spec.get
+        self.hidden, self.H, self.KV, self.D = int(g("hidden_size")), int(g("num_heads")), int(g("num_kv_heads")), int(g("head_dim"))
+        self.scale = float(g("scale"))
+        self.qk_norm = bool(g("qk_norm", False))
+        self.qk_eps = float(g("qk_norm_eps", 0.0))
+        self.window = g("window")
+        if self.H % self.KV:
+            raise ValueError(f"{self.H} query heads are not a multiple of {self.KV} kv heads")
+        self.qkv = self.o = self.q_norm = self.k_norm = None
+
+    def weight_specs(self):
+        H, KV, D, hid = self.H, self.KV, self.D, self.hidden
+        specs = [WeightSpec("q_proj", (H * D, hid)), WeightSpec("k_proj", (KV * D, hid)),
+                 WeightSpec("v_proj", (KV * D, hid)), WeightSpec("o_proj", (hid, H * D))]
+        if self.qk_norm:
+            specs += [WeightSpec("q_norm", (D,), kind="vector", init="norm"),
+                      WeightSpec("k_norm", (D,), kind="vector", init="norm")]
+        return specs
+
+    def cache_need(self):
+        return KVCacheNeed(self.KV, self.D, self.window)
+
+    def load(self, tensors, dtype, device):
+        self.qkv = torch.cat([tensors.pop("q_proj"), tensors.pop("k_proj"), tensors.pop("v_proj")], dim=0).contiguous()
+        self.o = tensors.pop("o_proj")
+        self.q_norm, self.k_norm = tensors.get("q_norm"), tensors.get("k_norm")
+
+    def forward(self, h, ctx, cache, position, owns_cache=True):
+        ops = ctx.ops
+        meta = ctx.batch.groups[cache.group]
+        qkv = ops.linear(h, self.qkv)
+        q = ops.qk_norm_rope_cache(
+            qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
+            position.rotary_inv_freq(), meta, cache.k if owns_cache else None,
+            cache.v if owns_cache else None)
+        o = ops.paged_attention(q, cache.k, cache.v, meta, self.H, self.KV, self.D, self.scale, self.window)
+        return ops.linear(o, self.o)

@@ -1,0 +1,30 @@
+"""SwiGLU feed-forward: down(silu(gate(h)) * up(h)) (engine/core/model_runner.py:124-131).
+gate and up are stored as one [2*inter, hidden] matrix so that one product serves both, as
+the reference does with FUSED_PROJ (engine/core/fused_linear.py:173-177,196)."""
+from __future__ import annotations
+
+import torch
+
+from .base import Part, WeightSpec, register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec.get("hidden_size"))
+        self.inter = int(spec.get("intermediate_size"))
+        self.gate_up = self.down = None
+
+    def weight_specs(self):
+        return [WeightSpec("gate_proj", (self.inter, self.hidden)),
+                WeightSpec("up_proj", (self.inter, self.hidden)),
+                WeightSpec("down_proj", (self.hidden, self.inter))]
+
+    def load(self, tensors, dtype, device):
+        self.gate_up = torch.cat([tensors.pop("gate_proj"), tensors.pop("up_proj")], dim=0).contiguous()
+        self.down = tensors.pop("down_proj")
+
+    def forward(self, h, ctx):
+        gu = ctx.ops.linear(h, self.gate_up)
+        return ctx.ops.linear(ctx.ops.swiglu(gu), self.down)

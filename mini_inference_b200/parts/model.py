@@ -1,0 +1,95 @@
+"""The generic decoder: embedding, the layers of a ModelSpec run in the spec's order, final
+norm on the rows whose logits are wanted, and the head (engine/core/model_runner.py:112-135).
+It is built from the spec alone; which family the spec came from is unknown here."""
+from __future__ import annotations
+
+from typing import Dict, List, Tuple
+
+import torch
+
+from ..config.spec import ModelSpec, PartSpec
+from .base import Part, WeightSpec, build_part
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self._positions: Dict = {}
+        self.blocks = []
+        self._owned: List[Tuple[str, WeightSpec, Part]] = []      # (checkpoint name, spec, owner)
+        for layer in spec.layers:
+            position = self._positions.get(layer.position)
+            if position is None:
+                position = self._positions[layer.position] = build_part("position", layer.position)
+            mixer = build_part("mixer", layer.mixer)
+            ffn = build_part("feed_forward", layer.feed_forward)
+            norm1, norm2 = build_part("norm", layer.norm), build_part("norm", layer.norm)
+            self.blocks.append(build_part("block", PartSpec.of(layer.block), mixer, ffn, norm1, norm2, position))
+            names = dict(layer.weight_names)
+            for role, part in (("mixer", mixer), ("feed_forward", ffn), ("norm1", norm1), ("norm2", norm2)):
+                for ws in part.weight_specs():
+                    key = f"{role}.{ws.name}"
+                    if key not in names:
+                        raise KeyError(f"the layer's weight_names has no entry for '{key}'")
+                    self._owned.append((names[key], ws, part))
+        self.final_norm = build_part("norm", spec.final_norm)
+        for ws in self.final_norm.weight_specs():
+            self._owned.append((spec.final_norm_name, ws, self.final_norm))
+        self.embedding = None
+        self.lm_head = None
+        self.dtype = None
+        self.device = None
+
+    # ---------------------------------------------------------------- weights
+    def weight_table(self) -> List[Tuple[str, WeightSpec]]:
+        """Every tensor the checkpoint must hold: (checkpoint name, spec)."""
+        table = [(self.spec.embedding_name, WeightSpec("embedding", (self.spec.vocab_size, self.spec.hidden_size)))]
+        table += [(name, ws) for name, ws, _ in self._owned]
+        if self.spec.lm_head_name is not None:
+            table.append((self.spec.lm_head_name, WeightSpec("lm_head", (self.spec.vocab_size, self.spec.hidden_size))))
+        return table
+
+    def ignorable_names(self):
+        """Tensors a checkpoint may hold that the model does not read (a tied head's copy)."""
+        return {"lm_head.weight"} if self.spec.lm_head_name is None else set()
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        """tensors: checkpoint name -> tensor already on the device in its runtime dtype."""
+        self.dtype, self.device = dtype, torch.device(device)
+        per_part: Dict[int, Dict[str, torch.Tensor]] = {}
+        for name, ws, part in self._owned:
+            per_part.setdefault(id(part), {})[ws.name] = tensors[name]
+        seen = set()
+        for _, _, part in self._owned:
+            if id(part) not in seen:
+                seen.add(id(part))
+                part.load(per_part[id(part)], dtype, self.device)
+        for position in self._positions.values():
+            position.load({}, dtype, self.device)
+        self.embedding = tensors[self.spec.embedding_name]
+        self.lm_head = self.embedding if self.spec.lm_head_name is None else tensors[self.spec.lm_head_name]
+
+    # ---------------------------------------------------------------- cache needs
+    def cache_needs(self):
+        """Per execution step: the mixer's need, or None when the step reads another's cache."""
+        needs = []
+        for step in self.spec.order:
+            needs.append(None if step.cache_from is not None else self.blocks[step.layer].mixer.cache_need())
+        return needs
+
+    # ---------------------------------------------------------------- one step
+    def forward(self, ctx, caches):
+        """caches[i]: LayerCache of execution step i.  Returns float32 logits for
+        ctx.batch.logit_rows, or None when no row wants logits."""
+        b, ops = ctx.batch, ctx.ops
+        x = ops.embedding(b.token_ids, self.embedding)
+        for position in self._positions.values():
+            x = position.on_embedding(x, ctx)
+        delta = None
+        for i, step in enumerate(self.spec.order):
+            src = i if step.cache_from is None else step.cache_from
+            x, delta = self.blocks[step.layer].forward(x, delta, ctx, caches[src], step.cache_from is None)
+        if b.num_logit_rows == 0:
+            return None
+        h = self.final_norm.forward(x, delta, ctx, rows=b.logit_rows)
+        return ops.linear(h, self.lm_head, out_dtype=torch.float32)

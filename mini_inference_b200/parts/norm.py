@@ -1,0 +1,24 @@
+"""RMSNorm: y = w * cast(x32 * rsqrt(mean(x32^2) + eps)), statistics in float32.  The
+reference calls the loaded model's norm modules (engine/core/model_runner.py:120-121,133);
+here the residual addition that precedes a norm is fused into the same kernel."""
+from __future__ import annotations
+
+from .base import Part, WeightSpec, register_norm
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(spec.get("size"))
+        self.eps = float(spec.get("eps"))
+        self.weight = None
+
+    def weight_specs(self):
+        return [WeightSpec("weight", (self.size,), kind="vector", init="norm")]
+
+    def load(self, tensors, dtype, device):
+        self.weight = tensors["weight"]
+
+    def forward(self, x, delta, ctx, rows=None):
+        return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows)

@@ -1,0 +1,54 @@
+"""Random-weights mode: write a model folder (config.json, model.safetensors) from a
+configuration and a seed.  The reference builds random models only in its tests
+(tests/test_models.py:55-62); here it is a mode of the loader, used by tests and benchmarks.
+
+Each tensor is drawn on the CPU in float32 from a generator seeded by (seed, tensor index),
+then stored in the requested dtype, so the same seed gives the same folder everywhere and a
+float32 run and a bfloat16 run of one folder hold the same values."""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from ..config.registry import resolve
+from ..parts.model import DecoderModel
+from .safetensors_io import write_safetensors
+
+_STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
+
+
+def _draw(ws, seed: int, index: int, std: float, norm_init: str) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed * 1_000_003 + index)
+    if ws.kind == "table":
+        return torch.zeros(ws.shape, dtype=torch.int32)
+    if ws.init == "norm":
+        if norm_init == "ones":
+            return torch.ones(ws.shape)
+        return torch.rand(ws.shape, generator=g) + 0.5            # U(0.5, 1.5)
+    if ws.init == "zeros":
+        return torch.zeros(ws.shape)
+    return torch.randn(ws.shape, generator=g) * std
+
+
+def write_random_model(config: dict, out_dir: str, seed: int = 0, std: float = 0.02,
+                       norm_init: str = "uniform", store_dtype: str = "bfloat16") -> str:
+    """config: the config.json dict of a registered architecture."""
+    arch = resolve(config)
+    cfg = arch.config_class.from_dict(config)
+    model = DecoderModel(arch.build_spec(cfg))
+    dtype = _STORE[store_dtype]
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        json.dump(cfg.to_dict() if hasattr(cfg, "to_dict") else config, f, indent=1)
+    items, seen = [], set()
+    for index, (name, ws) in enumerate(model.weight_table()):
+        if name in seen:
+            continue
+        seen.add(name)
+        store = torch.int32 if ws.kind == "table" else dtype
+        items.append((name, tuple(ws.shape), store,
+                      lambda ws=ws, index=index, store=store: _draw(ws, seed, index, std, norm_init).to(store)))
+    write_safetensors(os.path.join(out_dir, "model.safetensors"), items)
+    return out_dir
