@@ -1,0 +1,69 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MI_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes used across the C interface
+#define MI_F32 0
+#define MI_BF16 1
+
+namespace mi {
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// round through the storage type: what a value becomes when it is stored and read again
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, at most 1024); every thread gets the
+// same value, added in a fixed order so the result does not depend on what else runs.
+template <int NT> __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) total += scratch[w];
+    return total;
+}
+
+// 16 bytes of T: 4 floats or 8 bfloat16
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T> __device__ __forceinline__ void load16(const T* p, float* out) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    if constexpr (sizeof(T) == 4) {
+        out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+        out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+    } else {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {            // bf16 -> f32 is a shift into the high half
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+
+}  // namespace mi

@@ -1,0 +1,107 @@
+// Embedding gather, residual-add + RMSNorm, SwiGLU.
+//
+// Reference call sites (davidjoyme/mini-inference): engine/core/model_runner.py:115 (embed),
+// :120-121,133 (norms and residual additions), :124-127 (act(gate) * up).  The reference runs
+// each as several library kernels; here the residual addition is fused into the norm that
+// follows it, and the norm on the logit rows reads only those rows.
+#include "common.cuh"
+
+using namespace mi;
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                 int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;       // the host refuses such ids; never read out of range
+    const T* src = table + (size_t)id * hidden;
+    T* dst = out + (size_t)t * hidden;
+    constexpr int V = Vec16<T>::N;
+    if (hidden % V == 0) {
+        const uint4* s = reinterpret_cast<const uint4*>(src);
+        uint4* d = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < hidden / V; i += blockDim.x) d[i] = s[i];
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+MI_EXPORT int mi_embedding(const int* ids, const void* table, void* out, int T_, int hidden, int vocab,
+                           int dtype, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    if (dtype == MI_BF16)
+        embedding_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, hidden, vocab);
+    else
+        embedding_kernel<float><<<T_, 128, 0, stream>>>(ids, (const float*)table, (float*)out, hidden, vocab);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ (x += delta); y = rmsnorm(x) * w
+// One block per output row.  rows == nullptr: row r of x is updated in place with delta and
+// normalised.  rows != nullptr: output row r is the norm of x[rows[r]] (+ delta[rows[r]]),
+// x is left as it is.  The sum x + delta is formed in float32 and rounded to the stream's
+// type BEFORE its statistics are taken, as if it had been stored and read back.
+template <typename T, typename WT, int NT>
+__global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w,
+                                   T* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    T* xr = x + src;
+    const T* dr = delta ? delta + src : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += NT) {
+        float v = to_f32(xr[i]);
+        if (dr) {
+            v = round_to<T>(v + to_f32(dr[i]));
+            if (!rows) xr[i] = from_f32<T>(v);
+        }
+        ss += v * v;
+    }
+    const float total = block_sum<NT>(ss, scratch);
+    const float rstd = rsqrtf(total / (float)hidden + eps);
+    T* yr = y + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += NT) {
+        float v = to_f32(xr[i]);                         // in-place mode: this thread's own store above
+        if (dr && rows) v = round_to<T>(v + to_f32(dr[i]));
+        const float n = round_to<T>(v * rstd);
+        yr[i] = from_f32<T>(n * to_f32(w[i]));
+    }
+}
+
+MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
+                             int hidden, float eps, int dtype, int w_dtype, cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    constexpr int NT = 256;
+#define LAUNCH(T, WT) add_rmsnorm_kernel<T, WT, NT><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps)
+    if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);
+    else if (w_dtype == MI_F32) LAUNCH(float, float);
+    else return -1;
+#undef LAUNCH
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ silu(gate) * up
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    const size_t n = (size_t)rows * inter;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inter, c = i % inter;
+        const float g = to_f32(gate_up[r * 2 * inter + c]);
+        const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
+        out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+MI_EXPORT int mi_swiglu(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+    const size_t n = (size_t)rows * inter;
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == MI_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter);
+    else
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, inter);
+    return (int)cudaGetLastError();
+}

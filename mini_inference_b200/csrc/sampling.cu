@@ -1,0 +1,64 @@
+// Greedy and temperature sampling over float32 logits, one block per row.
+//
+// Reference (davidjoyme/mini-inference engine/core/sampler.py:3-11): argmax, or a draw from
+// softmax(logits / max(temperature, 1e-5)) with the library's global generator; rows with
+// temperature 0 take the argmax.  Here the draw is the Gumbel-max form of the same
+// distribution: argmax_i(logit_i / T + g_i), g_i = -log(-log(u_i)), with u_i from a counter
+// based hash of (request seed, tokens generated so far, i).  A request's draws therefore do
+// not depend on which other requests share its batch, and no probabilities are materialised.
+// Ties go to the lowest index, as argmax does on the host.
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ uint32_t fmix32(uint32_t h) {
+    h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+    return h;
+}
+
+__device__ __forceinline__ float gumbel(uint32_t seed, uint32_t counter, uint32_t i) {
+    uint32_t h = fmix32(i ^ (seed * 0x9E3779B1u));
+    h = fmix32(h ^ (counter * 0x85EBCA77u));
+    const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);     // in (0, 1)
+    return -logf(-logf(u));
+}
+
+template <int NT>
+__global__ void sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temps,
+                              const uint32_t* __restrict__ seeds, const uint32_t* __restrict__ counters,
+                              int* __restrict__ out) {
+    __shared__ float best_v[NT / 32];
+    __shared__ int best_i[NT / 32];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float temp = temps ? temps[r] : 0.f;
+    const bool draw = temp > 0.f;
+    const float inv_t = draw ? 1.f / fmaxf(temp, 1e-5f) : 1.f;
+    const uint32_t seed = draw ? seeds[r] : 0u, counter = draw ? counters[r] : 0u;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += NT) {
+        float v = row[i];
+        if (draw) v = v * inv_t + gumbel(seed, counter, (uint32_t)i);
+        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { best_v[threadIdx.x >> 5] = bv; best_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < NT / 32; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        out[r] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+MI_EXPORT int mi_sample(const float* logits, int ld, int rows, int vocab, const float* temps, const uint32_t* seeds,
+                        const uint32_t* counters, int* out, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    sample_kernel<1024><<<rows, 1024, 0, stream>>>(logits, ld, vocab, temps, seeds, counters, out);
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,180 @@
+"""Kernel namespace of the engine: thin Python entry points over the hand-written sm_100a
+kernels in csrc/ (built into _kernels.so, called through its C interface).
+
+There is no CPU path and no silent fall-back: get_ops() raises when there is no CUDA device
+or the library cannot be built or loaded.  Matrix products of the bfloat16 path go to the
+library GEMM, as the reference's do (engine/core/fused_linear.py:29-34); the float32 path
+uses this package's own float32 GEMM kernel, which never uses a reduced-precision mode.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+_LIB = None
+_c = ctypes
+
+
+def load_library():
+    global _LIB
+    if _LIB is None:
+        from .build import build
+        path = build()
+        _LIB = ctypes.CDLL(path)
+    return _LIB
+
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _code(dtype):
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise TypeError(f"dtype {dtype} is not supported by the kernels (float32, bfloat16)") from None
+
+
+def _p(t):
+    return _c.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(err, what):
+    if err != 0:
+        if err == -1:
+            raise TypeError(f"{what}: unsupported combination of dtypes")
+        if err == -2:
+            raise ValueError(f"{what}: size not supported by this kernel")
+        raise RuntimeError(f"{what}: CUDA error {err} at launch")
+
+
+class CudaOps:
+    prefill_tile = 64
+    NUM_SMS = 148
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError("mini_inference_b200 runs on a CUDA device only (no CPU path); "
+                               f"device '{device}' is not one")
+        self.lib = load_library()
+        self.force_splits = None             # tests set this to exercise the split merge on short contexts
+        self.launches = 0                    # kernels of this package launched so far
+
+    def _stream(self):
+        return _c.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # ---------------------------------------------------------------- elementwise / norms
+    def embedding(self, ids, table):
+        T, hidden = ids.shape[0], table.shape[1]
+        out = torch.empty((T, hidden), dtype=table.dtype, device=table.device)
+        _check(self.lib.mi_embedding(_p(ids), _p(table), _p(out), T, hidden, table.shape[0], _code(table.dtype),
+                                     self._stream()), "embedding")
+        self.launches += 1
+        return out
+
+    def add_rmsnorm(self, x, delta, weight, eps, rows=None):
+        hidden = x.shape[-1]
+        assert x.is_contiguous() and (delta is None or delta.is_contiguous())
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
+        _check(self.lib.mi_add_rmsnorm(_p(x), _p(delta), _p(weight), _p(y), _p(rows), n, hidden, _c.c_float(eps),
+                                       _code(x.dtype), _code(weight.dtype), self._stream()), "add_rmsnorm")
+        self.launches += 1
+        return y
+
+    def swiglu(self, gate_up):
+        rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+        assert gate_up.is_contiguous()
+        out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+        _check(self.lib.mi_swiglu(_p(gate_up), _p(out), rows, inter, _code(gate_up.dtype), self._stream()), "swiglu")
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- matrix products
+    def linear(self, x, w, out_dtype=None):
+        """x [M, K] (rows may be strided), w [N, K] -> [M, N]."""
+        if x.dtype == torch.float32:
+            M, K = x.shape
+            N = w.shape[0]
+            assert x.stride(1) == 1 and w.is_contiguous() and w.dtype == torch.float32
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+            _check(self.lib.mi_gemm_f32_nt(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, self._stream()), "gemm_f32")
+            self.launches += 1
+            return out
+        if out_dtype is not None and out_dtype != x.dtype:
+            try:
+                return torch.mm(x, w.t(), out_dtype=out_dtype)
+            except TypeError:
+                return torch.mm(x, w.t()).to(out_dtype)
+        return torch.mm(x, w.t())
+
+    # ---------------------------------------------------------------- q/k norm, rotation, cache write
+    def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):
+        T = qkv.shape[0]
+        assert qkv.is_contiguous() and qkv.shape[1] == (H + 2 * KV) * D
+        w_dtype = q_weight.dtype if q_weight is not None else qkv.dtype
+        _check(self.lib.mi_qk_norm_rope_cache(
+            _p(qkv), _p(q_weight), _p(k_weight), _p(inv_freq), _p(meta.positions), _p(meta.slots),
+            _p(k_cache), _p(v_cache), T, H, KV, D, meta.page_size, _c.c_float(eps), _code(qkv.dtype),
+            _code(w_dtype), self._stream()), "qk_norm_rope_cache")
+        self.launches += 1
+        return qkv[:, :H * D]
+
+    # ---------------------------------------------------------------- attention over the pages
+    def choose_splits(self, num_decode, H, max_kv_len):
+        if self.force_splits:
+            return self.force_splits
+        ctas = num_decode * math.ceil(H / 4)
+        return max(1, min(math.ceil(2 * self.NUM_SMS / ctas), math.ceil(max_kv_len / 256), 32))
+
+    def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
+        T = q.shape[0]
+        assert q.stride(1) == 1
+        out = torch.empty((T, H * D), dtype=q.dtype, device=q.device)
+        code, win = _code(q.dtype), int(window or 0)
+        if meta.num_prefill_tiles:
+            _check(self.lib.mi_attn_prefill_generic(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
+                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,
+                meta.page_size, meta.tile, _c.c_float(scale), win, code, self._stream()), "attn_prefill")
+            self.launches += 1
+        if meta.num_decode:
+            S = self.choose_splits(meta.num_decode, H, meta.max_kv_len)
+            o_part = lse = None
+            if S > 1:
+                o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)
+                lse = torch.empty((meta.num_decode, H, S), dtype=torch.float32, device=q.device)
+            _check(self.lib.mi_attn_decode_generic(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
+                meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, code, self._stream()), "attn_decode")
+            self.launches += 2 if S > 1 else 1
+        return out
+
+    # ---------------------------------------------------------------- sampling
+    def argmax(self, logits):
+        return self.sample(logits, None, None, None)
+
+    def sample(self, logits, temperatures, seeds, counters):
+        """logits float32 [R, V]; temperatures float32 [R] (0 = greedy); seeds, counters: int32
+        tensors read as unsigned.  Returns int32 [R]."""
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1
+        R, V = logits.shape
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        _check(self.lib.mi_sample(_p(logits), logits.stride(0), R, V, _p(temperatures), _p(seeds), _p(counters),
+                                  _p(out), self._stream()), "sample")
+        self.launches += 1
+        return out
+
+
+_OPS = {}
+
+
+def get_ops(device) -> CudaOps:
+    device = torch.device(device)
+    key = (device.type, device.index)
+    if key not in _OPS:
+        _OPS[key] = CudaOps(device)
+    return _OPS[key]

@@ -50,3 +50,61 @@ def random_tokens(vocab, n, seed):
 
 def rel_err(a, b):
     return ((a - b).abs().max() / b.abs().max().clamp_min(1e-30)).item()
+
+
+def check_cuts(runner, model_dir, vocab, tol, n=45, seed=5):
+    """whole prompt; most in one step + last 32 one by one; portions of changing size."""
+    ids = random_tokens(vocab, n, seed=seed)
+    want = plain_logits(model_dir, ids)
+    pool = runner.cache.free_pages()
+    whole = run_cuts(runner, "w", ids, [len(ids)])
+    assert rel_err(whole, want) < tol, ("whole", rel_err(whole, want))
+    dec = run_cuts(runner, "d", ids, [len(ids) - 32] + [1] * 32)
+    assert rel_err(dec, want) < tol, ("decode", rel_err(dec, want))
+    por = run_cuts(runner, "p", ids, random_cuts(len(ids), random.Random(1)))
+    assert rel_err(por, want) < tol, ("portions", rel_err(por, want))
+    first = run_cuts(runner, "f", ids[:3], [1, 1, 1])
+    assert rel_err(first, want[:3]) < tol, ("first tokens", rel_err(first, want[:3]))
+    runner.cache.check_invariants()
+    assert runner.cache.free_pages() == pool
+
+
+def check_mixed(make, model_dir, vocab, page, tol, lens=(23, 9, 31, 17, 40, 12, 27), seed=7):
+    """Up to four live requests, portions of some beside decoded tokens of others, a pool so
+    small that pages are used again."""
+    rng = random.Random(seed)
+    reqs = {f"r{i}": random_tokens(vocab, n, seed=100 + i) for i, n in enumerate(lens)}
+    want = {k: plain_logits(model_dir, v) for k, v in reqs.items()}
+    pool_tokens = 4 * 48
+    runner = make(pool_tokens // page)
+    pending = list(reqs)
+    live, got = {}, {k: [] for k in reqs}
+    while pending or live:
+        while pending and len(live) < 4:
+            k = pending.pop(0)
+            live[k] = [runner.cache.admit(k), 0]
+        entries, owners = [], []
+        for k, (seq, at) in live.items():
+            if rng.random() < 0.2 and len(live) > 1:
+                continue                                   # left out of this step
+            left = len(reqs[k]) - at
+            n = 1 if (at > 0 and rng.random() < 0.5) else min(left, rng.randint(2, 8))
+            if left - n == 1:
+                n = left
+            entries.append(StepEntry(seq, reqs[k][at:at + n], range(n)))
+            owners.append((k, n))
+        if not entries:
+            continue
+        logits = runner.step(entries).float().cpu()
+        row = 0
+        for k, n in owners:
+            got[k].append(logits[row:row + n])
+            row += n
+            live[k][1] += n
+        for k in [k for k, (seq, at) in live.items() if at == len(reqs[k])]:
+            runner.cache.free(live.pop(k)[0])
+        runner.cache.check_invariants()
+    for k in reqs:
+        e = rel_err(torch.cat(got[k]), want[k])
+        assert e < tol, (k, e)
+    assert runner.cache.free_pages() == pool_tokens // page

@@ -1,0 +1,201 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (tests/ref_ops.py), at sizes
+other than the engine's tiny configurations: widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd head counts and groups."""
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from tests.ref_ops import TorchRefOps
+from tests.ref_sampling import perturbed_scores
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_inference_b200.ops import get_ops
+    return get_ops(DEV)
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 1.6e-2
+
+
+def close(a, b, dtype, scale=None):
+    a, b = a.float(), b.float()
+    s = scale if scale is not None else b.abs().max().clamp_min(1e-6)
+    err = ((a - b).abs().max() / s).item()
+    assert err < tol(dtype), f"relative error {err}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(72, 301), (2560, 1000), (100, 77)])
+def test_embedding(ops, dtype, hidden, vocab):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, hidden, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (37,), generator=g).to(torch.int32).to(DEV)
+    assert torch.equal(ops.embedding(ids, table), TorchRefOps().embedding(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 2560, 1001])
+@pytest.mark.parametrize("w32", [False, True])
+def test_add_rmsnorm(ops, dtype, hidden, w32):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(19, hidden, generator=g) * 3).to(dtype).to(DEV)
+    d = torch.randn(19, hidden, generator=g).to(dtype).to(DEV)
+    w = (torch.rand(hidden, generator=g) + 0.5).to(torch.float32 if w32 else dtype).to(DEV)
+    ref = TorchRefOps()
+    for delta in (None, d):
+        x1, x2 = x.clone(), x.clone()
+        y1 = ops.add_rmsnorm(x1, delta, w, 1e-5)
+        y2 = ref.add_rmsnorm(x2, delta, w, 1e-5)
+        assert torch.equal(x1, x2)
+        close(y1, y2, dtype)
+        rows = torch.tensor([3, 0, 18, 7], dtype=torch.int32, device=DEV)
+        x3 = x.clone()
+        y3 = ops.add_rmsnorm(x3, delta, w, 1e-5, rows)
+        assert torch.equal(x3, x)
+        close(y3, ref.add_rmsnorm(x.clone(), delta, w, 1e-5, rows), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    g = torch.Generator().manual_seed(2)
+    gu = (torch.randn(13, 2 * 223, generator=g) * 4).to(dtype).to(DEV)
+    close(ops.swiglu(gu), TorchRefOps().swiglu(gu), dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 517, 96), (37, 130, 250), (64, 64, 16), (129, 65, 33)])
+def test_gemm_f32(ops, M, N, K):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K + 5, generator=g).to(DEV)[:, :K]          # strided rows
+    w = torch.randn(N, K, generator=g).to(DEV)
+    want = x.double() @ w.double().T
+    got = ops.linear(x, w)
+    assert ((got.double() - want).abs().max() / want.abs().max()).item() < 2e-6
+    # a row's result does not depend on the other rows of the batch
+    assert torch.equal(ops.linear(x[:1], w), got[:1])
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 301, 80), (64, 2560, 4096)])
+def test_linear_bf16(ops, M, N, K):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = TorchRefOps()
+    close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16)
+    out = ops.linear(x, w, out_dtype=torch.float32)
+    assert out.dtype == torch.float32
+    want = ref.linear(x, w, out_dtype=torch.float32)
+    assert ((out - want).abs().max() / want.abs().max()).item() < 1e-4
+
+
+def make_meta(page_size, segs, num_pages, seed, tile=64):
+    """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
+    shaped like engine.batch.GroupMeta."""
+    rng = np.random.default_rng(seed)
+    free = list(rng.permutation(np.arange(1, num_pages + 1)))
+    S = len(segs)
+    kv_len = [p + n for p, n in segs]
+    max_pages = max(-(-L // page_size) for L in kv_len)
+    table = np.zeros((S, max_pages), dtype=np.int32)
+    for s, L in enumerate(kv_len):
+        for i in range(-(-L // page_size)):
+            table[s, i] = free.pop()
+    q_start = np.zeros(S + 1, dtype=np.int32)
+    q_start[1:] = np.cumsum([n for _, n in segs])
+    positions = np.concatenate([np.arange(p, p + n) for p, n in segs]).astype(np.int32)
+    slots = np.concatenate([table[s, np.arange(p, p + n) // page_size] * page_size + np.arange(p, p + n) % page_size
+                            for s, (p, n) in enumerate(segs)]).astype(np.int32)
+    decode = [s for s, (_, n) in enumerate(segs) if n == 1]
+    tiles = [(s, r) for s, (_, n) in enumerate(segs) if n > 1 for r in range(0, n, tile)]
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
+    return types.SimpleNamespace(
+        page_size=page_size, tile=tile, positions=t(positions), slots=t(slots), block_table=t(table),
+        max_pages=max_pages, seg_q_start=t(q_start), seg_pos0=t([p for p, _ in segs]), seg_kv_len=t(kv_len),
+        decode_segs=t(decode), prefill_tiles=t(tiles).view(-1, 2), num_decode=len(decode),
+        num_prefill_tiles=len(tiles), max_kv_len=max(kv_len), num_tokens=int(q_start[-1]))
+
+
+ATTN_SHAPES = [  # H, KV, D, page
+    (4, 2, 16, 8), (6, 3, 32, 4), (5, 1, 48, 16), (8, 8, 64, 16), (32, 8, 128, 16), (3, 3, 80, 32), (2, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,D,page", ATTN_SHAPES)
+def test_qk_norm_rope_cache(ops, dtype, H, KV, D, page):
+    g = torch.Generator().manual_seed(5)
+    segs = [(0, 9), (37, 1), (5, 70)]
+    meta = make_meta(page, segs, 64, seed=1)
+    T = meta.num_tokens
+    qkv = torch.randn(T, (H + 2 * KV) * D, generator=g).to(dtype).to(DEV)
+    qw = (torch.rand(D, generator=g) + 0.5).to(dtype).to(DEV)
+    kw = (torch.rand(D, generator=g) + 0.5).to(dtype).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(DEV)
+    shape = (65, KV, page, D)
+    for use_norm, use_rope in ((True, True), (False, True), (True, False)):
+        k1, v1 = torch.zeros(shape, dtype=dtype, device=DEV), torch.zeros(shape, dtype=dtype, device=DEV)
+        k2, v2 = k1.clone(), v1.clone()
+        a = (qw, kw) if use_norm else (None, None)
+        f = inv_freq if use_rope else None
+        q1 = ops.qk_norm_rope_cache(qkv.clone(), H, KV, D, *a, 1e-6, f, meta, k1, v1)
+        q2 = TorchRefOps().qk_norm_rope_cache(qkv.clone(), H, KV, D, *a, 1e-6, f, meta, k2, v2)
+        close(q1, q2, dtype)
+        close(k1, k2, dtype)
+        assert torch.equal(v1, v2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,D,page", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 13])
+def test_paged_attention(ops, dtype, H, KV, D, page, window):
+    g = torch.Generator().manual_seed(6)
+    segs = [(0, 70), (150, 1), (31, 1), (40, 29), (0, 1), (299, 1), (3, 2)]
+    meta = make_meta(page, segs, 200, seed=2)
+    T = meta.num_tokens
+    q = torch.randn(T, H * D, generator=g).to(dtype).to(DEV)
+    kc = torch.randn(201, KV, page, D, generator=g).to(dtype).to(DEV)
+    vc = torch.randn(201, KV, page, D, generator=g).to(dtype).to(DEV)
+    # make one far key of the long decode stand out, so that a lost or misplaced key shows
+    kc[meta.block_table[5, 2].long(), :, 3, :] *= 4.0
+    want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+    for splits in (None, 1, 3):
+        ops.force_splits = splits
+        got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+        ops.force_splits = None
+        close(got, want, dtype)
+
+
+def test_sampling(ops):
+    g = torch.Generator().manual_seed(7)
+    V = 1543
+    logits = (torch.randn(6, V, generator=g) * 3).to(DEV)
+    logits[2, 100] = logits[2, 900] = logits[2].max() + 1          # a tie: the lowest index wins
+    assert torch.equal(ops.argmax(logits).cpu(), logits.argmax(-1).to(torch.int32).cpu())
+    assert int(ops.argmax(logits)[2]) == 100
+    temps = torch.tensor([0.0, 0.8, 1.5, 0.3, 0.0, 1.0], device=DEV)
+    seeds = torch.tensor([1, 2, 3, -5, 5, 6], dtype=torch.int32, device=DEV)
+    counters = torch.tensor([0, 1, 2, 3, 4, 70000], dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, temps, seeds, counters).cpu().long()
+    scores = perturbed_scores(logits.cpu(), temps.cpu(), seeds.cpu(), counters.cpu())
+    top = scores.max(-1).values
+    # the chosen token's perturbed score is the row's maximum (up to the rounding of log)
+    assert ((top - scores[torch.arange(6), got]).abs() < 1e-4 * top.abs().clamp_min(1)).all()
+    assert got[0] == logits[0].argmax().item() and got[4] == logits[4].argmax().item()
+
+
+def test_sampling_distribution(ops):
+    """Draws at temperature T follow softmax(logits / T): compare frequencies over many counters."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, 1.5, -3.0]], device=DEV).repeat(4096, 1)
+    temps = torch.full((4096,), 0.7, device=DEV)
+    seeds = torch.full((4096,), 1234, dtype=torch.int32, device=DEV)
+    counters = torch.arange(4096, dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, temps, seeds, counters).cpu().long()
+    freq = torch.bincount(got, minlength=7).float() / 4096
+    probs = torch.softmax(logits[0].cpu() / 0.7, -1)
+    assert (freq - probs).abs().max() < 0.03
