@@ -15,8 +15,21 @@ from concurrent.futures import ThreadPoolExecutor
 
 PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(PKG, "csrc")
-BUILD = os.path.join(PKG, "_build")
-LIB = os.path.join(PKG, "_kernels.so")
+
+
+def _out_dir() -> str:
+    """The package folder; a per-user folder under the temporary directory when the checkout
+    is read-only for this user."""
+    if os.access(PKG, os.W_OK):
+        return PKG
+    import tempfile
+    d = os.path.join(tempfile.gettempdir(), f"mini_inference_b200_build_{os.getuid()}")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
+BUILD = os.path.join(_out_dir(), "_build")
+LIB = os.path.join(_out_dir(), "_kernels.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
