@@ -1,0 +1,229 @@
+"""The Python entry point: model folder in, generated token ids out.
+
+The reference's CustomEngine (engine/custom_engine.py:19-330) wires loader, cache, runner,
+scheduler and sampler and runs the step loop on a background thread for its HTTP server.  The
+same wiring and the same loop body live here, driven synchronously by the caller:
+add_request() / step() / has_work(), or generate() for a list of prompts.  Token ids are the
+native interface (there is no tokenizer in this engine)."""
+from __future__ import annotations
+
+import time
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_args import EngineArgs
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .factory import DTYPES, load_model
+from .request import FINISHED, Request, SamplingParams
+from .runner import ModelRunner
+from .scheduler import Scheduler
+
+
+class LLM:
+    def __init__(self, model_dir: Optional[str], args: Optional[EngineArgs] = None, ops=None,
+                 random_config: Optional[dict] = None, random_seed: int = 0, random_std: float = 0.02, **overrides):
+        """model_dir: a folder with config.json and model.safetensors.  With model_dir=None and
+        random_config (a config.json dict) the weights are drawn on the device instead."""
+        args = args or EngineArgs()
+        for k, v in overrides.items():
+            if not hasattr(args, k):
+                raise TypeError(f"unknown engine setting '{k}'")
+            setattr(args, k, v)
+        args.__post_init__()
+        self.args = args
+        t0 = time.perf_counter()
+        if model_dir is not None:
+            self.config, self.model, self.load_info = load_model(model_dir, args.dtype, args.device)
+        else:
+            from ..config.registry import resolve
+            from ..parts.model import DecoderModel
+            from ..weights.random_init import init_random_on_device
+            arch = resolve(random_config)
+            self.config = arch.config_class.from_dict(random_config)
+            self.model = DecoderModel(arch.build_spec(self.config))
+            self.load_info = init_random_on_device(self.model, DTYPES[args.dtype], args.device, random_seed, random_std)
+        self.load_info["load_time_s"] = round(time.perf_counter() - t0, 3)
+        self.model_dir = model_dir
+        self.device, self.dtype = self.model.device, DTYPES[args.dtype]
+        # engine/custom_engine.py:28: the model's own limit, capped by MAX_MODEL_LEN
+        self.max_model_len = min(self.model.spec.max_position, args.max_model_len)
+        needs = self.model.cache_needs()
+        probe = CacheManager(needs, args.kv_block_size, 1, 1, args.kv_block_size, dtype=self.dtype, allocate=False)
+        tokens = self._kv_budget_tokens(probe.bytes_per_token())
+        num_pages = max(1, tokens // args.kv_block_size)
+        self.cache = CacheManager(needs, args.kv_block_size, num_pages, args.max_num_seqs,
+                                  min(self.max_model_len, num_pages * args.kv_block_size),
+                                  dtype=self.dtype, device=self.device, watermark=args.kv_watermark)
+        self.runner = ModelRunner(self.model, self.cache, ops)
+        self.ops = self.runner.ops
+        self.scheduler = Scheduler(self.cache, args.max_num_seqs, args.max_batched_tokens, self.max_model_len,
+                                   chunked_prefill=args.chunked_prefill)
+        self.sampler = Sampler(self.ops, args.seed)
+        self.eos_ids = set(self.model.spec.eos_token_ids)
+        self.graphs = None
+        if args.cuda_graphs:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self.runner, args.max_num_seqs)
+            self.graphs.capture()
+        self.last_error = None
+        # step wall time split by kind (engine/custom_engine.py:69,140-142)
+        self.step_time = {"decode": [0, 0.0], "other": [0, 0.0]}
+
+    # ---------------------------------------------------------------- setup
+    def _kv_budget_tokens(self, bytes_per_token: int) -> int:
+        """engine/custom_engine.py:105-121: fixed token count, fixed megabytes, or what the GPU
+        has left after the weights and a reserve for activations."""
+        a = self.args
+        if a.kv_cache_tokens:
+            return a.kv_cache_tokens
+        if a.kv_cache_mb:
+            return int(a.kv_cache_mb * 1024 ** 2 // max(bytes_per_token, 1))
+        if self.device.type != "cuda":
+            return 32768
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = total * a.gpu_memory_utilization - (total - free) - a.activation_reserve_gb * 1024 ** 3
+        return max(int(max(budget, 0) // max(bytes_per_token, 1)), 1024)
+
+    # ---------------------------------------------------------------- requests
+    def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None) -> Request:
+        ids = [int(t) for t in prompt_ids]
+        if not ids:
+            raise ValueError("the prompt is empty")                       # engine/custom_engine.py:189-190
+        if min(ids) < 0 or max(ids) >= self.model.spec.vocab_size:
+            raise ValueError(f"token id outside [0, {self.model.spec.vocab_size})")
+        limit = min(self.max_model_len, self.cache.capacity_tokens)
+        if len(ids) >= limit:
+            raise ValueError(f"prompt is {len(ids)} tokens; the limit is {limit - 1}")   # :191-193
+        params = params or SamplingParams(max_new_tokens=self.args.max_new_tokens)
+        params = SamplingParams(max_new_tokens=min(params.max_new_tokens, limit - len(ids)),
+                                temperature=params.temperature, seed=params.seed, ignore_eos=params.ignore_eos)
+        req = Request(prompt_ids=ids, params=params)
+        self.scheduler.add(req)
+        return req
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ---------------------------------------------------------------- the loop body
+    def step(self) -> List[Request]:
+        """Schedule, run, sample, deliver (engine/custom_engine.py:124-170).  Returns the
+        requests that finished in this step."""
+        now = time.perf_counter()
+        chunks = self.scheduler.schedule(now)
+        if not chunks:
+            return self._fail_unschedulable()
+        start = time.perf_counter()
+        try:
+            tokens = self._run(chunks)
+        except Exception as e:                                           # fail this batch, keep serving
+            self.last_error = f"{type(e).__name__}: {e}"
+            done = self.scheduler.abort_all()
+            for r in done:
+                self._finish(r, "error", error=self.last_error)
+            return done
+        kind = "decode" if all(e - s == 1 and s > 0 for _, s, e in chunks) else "other"
+        self.step_time[kind][0] += 1
+        self.step_time[kind][1] += (time.perf_counter() - start) * 1e3
+        now = time.perf_counter()
+        done, row = [], 0
+        for req, _, end in chunks:
+            req.num_computed = end
+            if end < req.total_len:                                      # prompt not finished yet
+                continue
+            tok = tokens[row]
+            row += 1
+            req.output_ids.append(tok)
+            if req.first_token_at is None:
+                req.first_token_at = now
+            req.token_times.append(now)
+            eos = tok in self.eos_ids and not req.params.ignore_eos
+            if eos or len(req.output_ids) >= req.params.max_new_tokens or req.total_len >= self.max_model_len:
+                self.scheduler.finish(req)
+                self._finish(req, "stop" if eos else "length")
+                done.append(req)
+        return done
+
+    def _run(self, chunks) -> List[int]:
+        if self.graphs is not None:
+            out = self.graphs.run(chunks, self.sampler)
+            if out is not None:
+                return out
+        entries, sampled = [], []
+        for req, s, e in chunks:
+            last = e == req.total_len
+            entries.append(StepEntry(req.seq, req.all_ids[s:e], [e - s - 1] if last else []))
+            if last:
+                sampled.append(req)
+        logits = self.runner.step(entries, ensure=False)
+        if logits is None:
+            return []
+        return self.sampler.sample(logits, sampled).tolist()             # the step's one device->host sync
+
+    def _finish(self, req, reason, error=None):
+        req.state, req.finish_reason, req.error = FINISHED, reason, error
+        req.finished_at = time.perf_counter()
+
+    def _fail_unschedulable(self):
+        """Nothing could be scheduled.  If nothing runs either, the request at the head of the
+        queue can never fit (its pages plus the watermark exceed the pool): fail it instead of
+        spinning."""
+        if self.scheduler.running or not self.scheduler.waiting:
+            return []
+        req = self.scheduler.waiting.popleft()
+        self._finish(req, "error", error=f"request of {req.total_len} tokens does not fit in the cache "
+                                         f"({self.cache.capacity_tokens} tokens)")
+        return [req]
+
+    # ---------------------------------------------------------------- public API
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        """Token ids in, generated token ids out, one list per prompt."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        for r in reqs:
+            if r.error:
+                raise RuntimeError(f"request {r.id} failed: {r.error}")
+        return [list(r.output_ids) for r in reqs]
+
+    def score(self, token_ids: Sequence[int]) -> torch.Tensor:
+        """float32 logits for every position, through the paged cache (engine/custom_engine.py:279-296)."""
+        seq = self.cache.admit(("score", id(token_ids)), len(token_ids))
+        if seq is None:
+            raise RuntimeError("not enough free cache to score this sequence")
+        try:
+            return self.runner.step([StepEntry(seq, token_ids, range(len(token_ids)))])
+        finally:
+            self.cache.free(seq)
+
+    def stats(self) -> dict:
+        t = {"decode_steps_timed": self.step_time["decode"][0],
+             "decode_step_ms_total": round(self.step_time["decode"][1], 3),
+             "other_steps_timed": self.step_time["other"][0],
+             "other_step_ms_total": round(self.step_time["other"][1], 3)}
+        g = self.graphs.stats() if self.graphs is not None else {}
+        return {**self.scheduler.stats(), **self.cache.stats(), **g, **t}
+
+    def info(self) -> dict:
+        """What the reference records in every result file (engine/base.py:35-49,
+        engine/custom_engine.py:298-321)."""
+        return {
+            "engine": "mini_inference_b200", "model": self.model_dir, "architecture": self.config.architecture,
+            "dtype": self.args.dtype, "max_model_len": self.max_model_len, "scheduler": "continuous",
+            "kv_cache": "paged", "kv_block_size": self.args.kv_block_size, "kv_watermark": self.args.kv_watermark,
+            "kv_capacity_tokens": self.cache.capacity_tokens,
+            "kv_cache_mb": round(self.cache.capacity_tokens * self.cache.bytes_per_token() / 1024 ** 2, 1),
+            "max_num_seqs": self.args.max_num_seqs, "max_batched_tokens": self.args.max_batched_tokens,
+            "chunked_prefill": self.args.chunked_prefill, "cuda_graphs": self.graphs is not None,
+            "weights": self.load_info,
+        }
+
+
+def create_engine(model_dir: str, **settings) -> LLM:
+    """Counterpart of the reference's create_engine() (engine/factory.py:5-10)."""
+    return LLM(model_dir, **settings)

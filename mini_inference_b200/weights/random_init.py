@@ -52,3 +52,25 @@ def write_random_model(config: dict, out_dir: str, seed: int = 0, std: float = 0
                       lambda ws=ws, index=index, store=store: _draw(ws, seed, index, std, norm_init).to(store)))
     write_safetensors(os.path.join(out_dir, "model.safetensors"), items)
     return out_dir
+
+
+def init_random_on_device(model, dtype: torch.dtype, device, seed: int = 0, std: float = 0.02,
+                          norm_init: str = "ones") -> dict:
+    """Random weights drawn directly on the device, tensor by tensor (benchmarks of large
+    configurations: no folder is written, nothing passes through host memory)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    tensors, nbytes = {}, 0
+    for name, ws in model.weight_table():
+        if name in tensors:
+            continue
+        if ws.kind == "table":
+            t = torch.zeros(ws.shape, dtype=torch.int32, device=device)
+        elif ws.init == "norm":
+            t = torch.ones(ws.shape, dtype=dtype, device=device) if norm_init == "ones" else \
+                (torch.rand(ws.shape, generator=g, device=device) + 0.5).to(dtype)
+        else:
+            t = torch.empty(ws.shape, dtype=dtype, device=device).normal_(0.0, std, generator=g)
+        tensors[name] = t
+        nbytes += t.numel() * t.element_size()
+    model.load(tensors, dtype, device)
+    return {"tensors": len(tensors), "weight_bytes": nbytes}
