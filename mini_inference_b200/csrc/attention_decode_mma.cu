@@ -1,0 +1,232 @@
+// Split-KV paged decode attention on the tensor cores, bfloat16, head size 64 or 128.
+//
+// Reference (davidjoyme/mini-inference kernels/paged_attention/decode_triton.py:6-100): one
+// program per (request, QUERY head, split) that multiplies k * q element by element on the
+// CUDA cores; the 4 query heads that share a kv head each read the same keys again.  Here one
+// block serves (request, KV head, split): the G query heads of the group are the rows of a
+// 16-row mma tile, so each key and value is read from HBM once per group.
+//
+// Data path: no shared-memory staging.  Each thread loads 16-byte pieces of K and V straight
+// from the pages into the registers that mma.sync.m16n8k16 wants.  That works because the
+// reduction index of a dot product may be permuted freely: for the scores the head dimension
+// is permuted so that the 8 values a thread feeds to two k-steps are 8 CONSECUTIVE values of
+// one key (one 16-byte load; a warp instruction covers 8 keys x 64 B); the query fragments use
+// the same permutation.  For P*V the output columns are permuted the same way (column g of
+// tile t is d = 8g + t), so a thread's 16-byte load of one value row serves 8 output tiles; a
+// byte permute pairs the rows of two keys into one B register.
+//
+// Each of the 4 warps takes every 4th 16-key block of the split's range with its own running
+// (max, sum, output); the warps are merged through shared memory at the end, the splits by
+// mi_attn_decode_merge (attention_generic.cu) when there is more than one.
+// Needs page_size % 16 == 0 (a 16-key block never straddles a page) and G <= 16.
+#include "common.cuh"
+#include <math.h>
+
+using namespace mi;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int DEC_WARPS = 4;
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+                       const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
+                       const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
+                       const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
+                       float scale_log2, int window) {
+    constexpr int KS = D / 16;          // k-steps of the score product
+    constexpr int NT = D / 8;           // output tiles of 8 columns
+    constexpr int HALVES = D / 64;      // 64-column halves of a value row
+    extern __shared__ float smem[];     // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int G = H / KV;
+    const int seg = decode_segs[blockIdx.x], kvh = blockIdx.y;
+    const int S = gridDim.z, s = blockIdx.z;
+    const int tok = seg_q_start[seg], len = seg_kv_len[seg];
+    const int lo = window > 0 ? max(0, len - window) : 0;
+    const int blk_lo = lo / 16, blk_hi = (len + 15) / 16;
+    const int per = (blk_hi - blk_lo + S - 1) / S;
+    const int b0 = blk_lo + s * per, b1 = min(b0 + per, blk_hi);
+    const int* table_row = block_table + (size_t)seg * table_stride;
+
+    // query fragments, permuted: the 16 bytes at d = 32 j + 8 c of rows g and g + 8
+    uint32_t qa[KS][4];
+    {
+        const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
+#pragma unroll
+        for (int j = 0; j < KS / 2; ++j) {
+            uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
+            if (g < G) r0 = *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + 32 * j + 8 * c);
+            if (g + 8 < G) r1 = *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + 32 * j + 8 * c);
+            qa[2 * j][0] = r0.x; qa[2 * j][2] = r0.y; qa[2 * j + 1][0] = r0.z; qa[2 * j + 1][2] = r0.w;
+            qa[2 * j][1] = r1.x; qa[2 * j][3] = r1.y; qa[2 * j + 1][1] = r1.z; qa[2 * j + 1][3] = r1.w;
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows g and g + 8; sums are per thread
+
+    uint4 kreg[2][KS / 2];
+    auto load_k = [&](int blk) {
+        const int page = table_row[(blk * 16) / ps];
+        const __nv_bfloat16* base = k_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int j = 0; j < KS / 2; ++j)
+                kreg[nt][j] = *reinterpret_cast<const uint4*>(base + (size_t)(nt * 8 + g) * D + 32 * j + 8 * c);
+    };
+
+    int blk = b0 + warp;
+    if (blk < b1) load_k(blk);
+    for (; blk < b1; blk += DEC_WARPS) {
+        // values of this block: rows of keys 2c, 2c+1, 2c+8, 2c+9, 16 bytes at d = 64 hb + 8 g
+        uint4 vreg[4][HALVES];
+        {
+            const int page = table_row[(blk * 16) / ps];
+            const __nv_bfloat16* base = v_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = 2 * c + (i & 1) + 8 * (i >> 1);
+#pragma unroll
+                for (int hb = 0; hb < HALVES; ++hb)
+                    vreg[i][hb] = *reinterpret_cast<const uint4*>(base + (size_t)key * D + 64 * hb + 8 * g);
+            }
+        }
+        // scores: 16 (heads) x 16 (keys) as two 8-key tiles
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < KS / 2; ++j) {
+                mma_bf16_16816(sc[nt], qa[2 * j], kreg[nt][j].x, kreg[nt][j].y);
+                mma_bf16_16816(sc[nt], qa[2 * j + 1], kreg[nt][j].z, kreg[nt][j].w);
+            }
+        }
+        if (blk + DEC_WARPS < b1) load_k(blk + DEC_WARPS);          // next block's keys fly during the rest
+        // mask, online softmax (base 2)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = blk * 16 + nt * 8 + 2 * c + e;
+                const bool ok = key >= lo && key < len;
+                sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
+                sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, sc[nt][e]);
+                mx1 = fmaxf(mx1, sc[nt][2 + e]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);      // finite: every block holds a visible key
+        const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        l0 *= al0; l1 *= al1;
+        uint32_t pa[4];
+        {
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                p[nt][0] = exp2f(sc[nt][0] - n0); p[nt][1] = exp2f(sc[nt][1] - n0);
+                p[nt][2] = exp2f(sc[nt][2] - n1); p[nt][3] = exp2f(sc[nt][3] - n1);
+                l0 += p[nt][0] + p[nt][1];
+                l1 += p[nt][2] + p[nt][3];
+            }
+            pa[0] = pack_bf16(p[0][0], p[0][1]); pa[1] = pack_bf16(p[0][2], p[0][3]);
+            pa[2] = pack_bf16(p[1][0], p[1][1]); pa[3] = pack_bf16(p[1][2], p[1][3]);
+        }
+        // O += P V; tile t of half hb: column g is d = 64 hb + 8 g + t
+#pragma unroll
+        for (int hb = 0; hb < HALVES; ++hb) {
+            const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vreg[0][hb]);   // key 2c
+            const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vreg[1][hb]);   // key 2c + 1
+            const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vreg[2][hb]);   // key 2c + 8
+            const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vreg[3][hb]);   // key 2c + 9
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+                const uint32_t vb0 = __byte_perm(r0[t >> 1], r1[t >> 1], sel);
+                const uint32_t vb1 = __byte_perm(r2[t >> 1], r3[t >> 1], sel);
+                float (&acc)[4] = o[hb * 8 + t];
+                acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1;
+                mma_bf16_16816(acc, pa, vb0, vb1);
+            }
+        }
+    }
+
+    // row sums over the quad, then merge the warps
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* so = smem + (size_t)warp * 16 * D;
+    float* sm = smem + (size_t)DEC_WARPS * 16 * D;
+    float* sl = sm + DEC_WARPS * 16;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int d0 = 64 * (t >> 3) + 8 * (2 * c) + (t & 7), d1 = d0 + 8;
+        so[g * D + d0] = o[t][0]; so[g * D + d1] = o[t][1];
+        so[(g + 8) * D + d0] = o[t][2]; so[(g + 8) * D + d1] = o[t][3];
+    }
+    if (c == 0) {
+        sm[warp * 16 + g] = m0; sl[warp * 16 + g] = l0;
+        sm[warp * 16 + g + 8] = m1; sl[warp * 16 + g + 8] = l1;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+        const int row = idx / D, d = idx % D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, sm[w * 16 + row]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = sm[w * 16 + row] == -INFINITY ? 0.f : exp2f(sm[w * 16 + row] - mx);
+            num += f * smem[((size_t)w * 16 + row) * D + d];
+            den += f * sl[w * 16 + row];
+        }
+        const float val = den > 0.f ? num / den : 0.f;
+        const int h = kvh * G + row;
+        if (S == 1) {
+            out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t pi = ((size_t)blockIdx.x * H + h) * S + s;
+            o_part[pi * D + d] = val;
+            if (d == 0) lse_part[pi] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
+        }
+    }
+}
+
+MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                 float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                 const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                 int table_stride, int H, int KV, int D, int ps, int splits, float scale, int window,
+                                 cudaStream_t stream) {
+    if (num_decode == 0) return 0;
+    if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
+    dim3 grid(num_decode, KV, splits);
+    const size_t smem = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
+    const float scale_log2 = scale * 1.4426950408889634f;
+#define LAUNCH(DD) do { \
+        attn_decode_mma_kernel<DD><<<grid, DEC_WARPS * 32, smem, stream>>>( \
+            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+            (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
+            H, KV, ps, scale_log2, window); } while (0)
+    if (D == 128) LAUNCH(128); else LAUNCH(64);
+#undef LAUNCH
+    return (int)cudaGetLastError();
+}

@@ -204,3 +204,15 @@ MI_EXPORT int mi_attn_decode_generic(const void* q, int q_stride, const void* k_
         attn_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, D, splits);
     return (int)cudaGetLastError();
 }
+
+MI_EXPORT int mi_attn_decode_merge(const float* o_part, const float* lse_part, void* out, const int* decode_segs,
+                                   int num_decode, const int* seg_q_start, int H, int D, int splits, int dtype,
+                                   cudaStream_t stream) {
+    if (num_decode == 0) return 0;
+    dim3 mgrid(num_decode, H);
+    if (dtype == MI_BF16)
+        attn_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, H, D, splits);
+    else
+        attn_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, D, splits);
+    return (int)cudaGetLastError();
+}

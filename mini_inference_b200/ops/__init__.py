@@ -60,6 +60,7 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
+        self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -123,10 +124,11 @@ class CudaOps:
         return qkv[:, :H * D]
 
     # ---------------------------------------------------------------- attention over the pages
-    def choose_splits(self, num_decode, H, max_kv_len):
+    def choose_splits(self, ctas, max_kv_len):
+        """Enough blocks to fill the GPU about twice, never more splits than the longest
+        request has 256-key pieces (kernels/paged_attention/decode_triton.py:114-120)."""
         if self.force_splits:
             return self.force_splits
-        ctas = num_decode * math.ceil(H / 4)
         return max(1, min(math.ceil(2 * self.NUM_SMS / ctas), math.ceil(max_kv_len / 256), 32))
 
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
@@ -134,18 +136,37 @@ class CudaOps:
         assert q.stride(1) == 1
         out = torch.empty((T, H * D), dtype=q.dtype, device=q.device)
         code, win = _code(q.dtype), int(window or 0)
-        if meta.num_prefill_tiles:
+        fast = (self.fast_attention and q.dtype == torch.bfloat16 and D in (64, 128) and q.stride(0) % 8 == 0
+                and q.data_ptr() % 16 == 0)
+        if meta.num_prefill_tiles and fast and meta.tile == 64:
+            _check(self.lib.mi_attn_prefill_mma(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
+                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,
+                meta.page_size, meta.tile, _c.c_float(scale), win, self._stream()), "attn_prefill_mma")
+            self.launches += 1
+        elif meta.num_prefill_tiles:
             _check(self.lib.mi_attn_prefill_generic(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
                 _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,
                 meta.page_size, meta.tile, _c.c_float(scale), win, code, self._stream()), "attn_prefill")
             self.launches += 1
+        fast_decode = fast and H // KV <= 16 and meta.page_size % 16 == 0
         if meta.num_decode:
-            S = self.choose_splits(meta.num_decode, H, meta.max_kv_len)
+            S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len)
             o_part = lse = None
             if S > 1:
                 o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)
                 lse = torch.empty((meta.num_decode, H, S), dtype=torch.float32, device=q.device)
+        if meta.num_decode and fast_decode:
+            _check(self.lib.mi_attn_decode_mma(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
+                meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, self._stream()), "attn_decode_mma")
+            if S > 1:
+                _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,
+                                                     _p(meta.seg_q_start), H, D, S, code, self._stream()), "attn_merge")
+            self.launches += 2 if S > 1 else 1
+        elif meta.num_decode:
             _check(self.lib.mi_attn_decode_generic(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,

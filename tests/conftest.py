@@ -43,7 +43,14 @@ TINY_W = {
     "max_position_embeddings": 512, "use_sliding_window": True, "sliding_window": 11,
     "layer_types": ["sliding_attention", "full_attention", "sliding_attention"],
 }
-TINY = {"A": (TINY_A, dict(seed=0, std=0.02), 8), "B": (TINY_B, dict(seed=1, std=0.05), 4),
+# A fourth one whose head size (64) and page size (16) reach the tensor-core attention kernels.
+TINY_F = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 200,
+    "vocab_size": 333, "rope_theta": 300000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 2048,
+}
+TINY = {"F": (TINY_F, dict(seed=4, std=0.06), 16), "A": (TINY_A, dict(seed=0, std=0.02), 8), "B": (TINY_B, dict(seed=1, std=0.05), 4),
         "W": (TINY_W, dict(seed=2, std=0.08), 4)}
 
 

@@ -12,14 +12,14 @@ TOLS = {"float32": 2e-5, "bfloat16": 4e-2}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "F"])
 def test_whole_decode_and_portions(tiny_dirs, name, dtype):
     d, cfg, page = tiny_dirs[name]
     check_cuts(make_engine(d, page, 64, dtype=dtype, device=DEV), d, cfg["vocab_size"], TOLS[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "F"])
 def test_mixed_batches_reuse_pages(tiny_dirs, name, dtype):
     d, cfg, page = tiny_dirs[name]
     check_mixed(lambda pages: make_engine(d, page, pages, dtype=dtype, device=DEV), d, cfg["vocab_size"], page,
@@ -27,7 +27,7 @@ def test_mixed_batches_reuse_pages(tiny_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["B", "W"])
+@pytest.mark.parametrize("name", ["B", "W", "F"])
 def test_long_decoding(tiny_dirs, name, dtype):
     """A short prompt and 300 tokens one by one: several splits, many pages, window edges."""
     d, cfg, page = tiny_dirs[name]

@@ -123,7 +123,8 @@ def make_meta(page_size, segs, num_pages, seed, tile=64):
 
 
 ATTN_SHAPES = [  # H, KV, D, page
-    (4, 2, 16, 8), (6, 3, 32, 4), (5, 1, 48, 16), (8, 8, 64, 16), (32, 8, 128, 16), (3, 3, 80, 32), (2, 1, 256, 16)]
+    (4, 2, 16, 8), (6, 3, 32, 4), (5, 1, 48, 16), (8, 8, 64, 16), (32, 8, 128, 16), (3, 3, 80, 32), (2, 1, 256, 16),
+    (5, 1, 64, 16), (12, 1, 128, 32), (16, 1, 64, 16), (6, 2, 128, 8), (20, 1, 128, 16)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -164,11 +165,14 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
     # make one far key of the long decode stand out, so that a lost or misplaced key shows
     kc[meta.block_table[5, 2].long(), :, 3, :] *= 4.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-    for splits in (None, 1, 3):
-        ops.force_splits = splits
-        got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-        ops.force_splits = None
-        close(got, want, dtype)
+    for fast in (True, False):
+        for splits in (None, 1, 3):
+            ops.force_splits, ops.fast_attention = splits, fast
+            try:
+                got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+            finally:
+                ops.force_splits, ops.fast_attention = None, True
+            close(got, want, dtype)
 
 
 def test_sampling(ops):

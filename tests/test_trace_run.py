@@ -103,7 +103,7 @@ def test_trace_run_cpu(tiny_dirs, tmp_path, monkeypatch, capsys, name, way):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "F"])
 def test_trace_run_gpu(tiny_dirs, tmp_path, name, dtype, tol):
     d, cfg, _ = tiny_dirs[name]
     reqs, tr = traces(cfg["vocab_size"])
