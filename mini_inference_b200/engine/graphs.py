@@ -78,7 +78,6 @@ class DecodeGraphs:
         logits = self.runner.model.forward(ctx, self.cache.layer_caches)
         return self.ops.sample(logits, batch.temps, batch.seeds, batch.counters)
 
-    @torch.inference_mode()
     def capture(self):
         import time
         t0 = time.perf_counter()
