@@ -185,6 +185,46 @@ def prefill(llm, torch, tokens, vocab, warmup=3, reps=3):
     return min(times)
 
 
+def profile(args, cfg, torch, LLM):
+    """A small, bounded run for a profiler: no prefill before the decode steps (the cache holds
+    zeros at the benchmark's context length), one graph bucket, few launches."""
+    from mini_inference_b200.engine.batch import StepEntry
+    from mini_inference_b200.engine.graphs import DecodeGraphs
+    vocab = cfg["vocab_size"]
+    llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
+              kv_cache_tokens=args.batch * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=args.batch,
+              max_model_len=args.ctx, max_batched_tokens=4096, cuda_graphs=False)
+    if args.profile == "prefill":
+        ms = prefill(llm, torch, 2048, vocab, warmup=1, reps=args.steps)
+        print(f"prefill 2048 tokens: {ms:.3f} ms")
+        return 0
+    llm.graphs = DecodeGraphs(llm.runner, args.batch, buckets=[args.batch])
+    llm.graphs.capture()
+    seqs = []
+    for i in range(args.batch):
+        seq = llm.cache.admit(("p", i), args.ctx)
+        llm.cache.ensure(seq, args.ctx - args.steps - args.warmup - 1)
+        llm.cache.commit(seq, args.ctx - args.steps - args.warmup - 1)
+        seqs.append(seq)
+    G, B = llm.graphs, args.batch
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(args.warmup + args.steps):
+        if i == args.warmup:
+            start.record()
+        for s in seqs:
+            llm.cache.ensure(s, s.num_tokens + 1)
+        G.fill(B, seqs, [1] * B if i == 0 else None)
+        G.replay(B)
+        G.feed_back(B)
+        for s in seqs:
+            llm.cache.commit(s, s.num_tokens + 1)
+    stop.record()
+    torch.cuda.synchronize()
+    print(f"decode b{B} ctx{args.ctx}: {start.elapsed_time(stop) / args.steps:.3f} ms/step, "
+          f"{G.launches[B]} own kernels per step")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -195,6 +235,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+                    help="run only a few decode steps (cache filled without a prefill) or one prefill, for ncu")
     args = ap.parse_args()
     if args.gpus > 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported (use --gpus 1)")
@@ -215,6 +257,8 @@ def main():
     pk = peaks()
     nums = model_numbers(cfg, args.layers)
     kv_tokens = max(64, args.batch) * args.ctx + 4096
+    if args.profile:
+        return profile(args, cfg, torch, LLM)
     llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
               kv_cache_tokens=kv_tokens, kv_watermark=0.0, max_num_seqs=max(64, args.batch), max_model_len=args.ctx,
               max_batched_tokens=4096, cuda_graphs=True)

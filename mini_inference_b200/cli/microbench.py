@@ -1,0 +1,115 @@
+"""Microbenchmarks of the decode step's bandwidth-bound kernels, in the manner of the
+reference's bench/micro/bench_gemm.py (:35-170: every linear of a model at a few row counts,
+ms, GB/s and share of peak, rotating weight copies to defeat the L2) and
+bench/micro/bench_attention.py (:61-167: paged decode attention over batch x context).
+
+    python -m mini_inference_b200.cli.microbench gemm      [--rows 1,8,64] [--size 4b]
+    python -m mini_inference_b200.cli.microbench attention [--batch 1,8,64] [--ctx 4096]
+
+Each line: kernel, shape, microseconds (CUDA events, after warm-up), GB/s of the bytes the
+kernel has to read, and that as a share of the measured copy bandwidth."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import types
+
+import torch
+
+from .run_engine import SIZES
+
+
+def peak_gbs():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return json.load(f)["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def timed(fn, iters, warmup=5):
+    for _ in range(warmup):
+        fn(0)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(iters):
+        fn(i)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / iters          # microseconds
+
+
+def bench_gemm(args, ops, peak):
+    cfg = SIZES[args.size]
+    h, H, KV, D, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                         cfg["intermediate_size"], cfg["vocab_size"])
+    shapes = [("qkv", (H + 2 * KV) * D, h), ("o", h, H * D), ("gate_up", 2 * I, h), ("down", h, I), ("lm_head", V, h)]
+    for name, N, K in shapes:
+        copies = max(2, -(-args.rotate_mb * 2 ** 20 // (N * K * 2)))      # rotate >= rotate_mb of weights
+        ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        for M in args.rows:
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            od = torch.float32 if name == "lm_head" else None
+            for label, flag in (("own", True), ("library", False)):
+                ops.skinny_gemm = flag
+                us = timed(lambda i: ops.linear(x, ws[i % copies], out_dtype=od), args.iters)
+                gbs = N * K * 2 / us / 1e3
+                print(f"gemm {name:8s} M={M:<3d} N={N:<6d} K={K:<5d} {label:8s} {us:9.2f} us {gbs:8.1f} GB/s "
+                      f"{100 * gbs / peak:5.1f} % of peak", flush=True)
+            ops.skinny_gemm = True
+        del ws
+
+
+def bench_attention(args, ops, peak):
+    cfg = SIZES[args.size]
+    H, KV, D, ps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], args.page_size
+    for B in args.batch:
+        pages_per_seq = -(-args.ctx // ps)
+        layers = max(2, -(-args.rotate_mb * 2 ** 20 // (B * pages_per_seq * ps * KV * D * 4)))
+        num_pages = B * pages_per_seq
+        kv = torch.randn(layers, 2, num_pages + 1, KV, ps, D, device="cuda", dtype=torch.bfloat16)
+        perm = torch.randperm(num_pages, device="cuda").to(torch.int32) + 1
+        table = perm.view(B, pages_per_seq).contiguous()
+        ar = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        meta = types.SimpleNamespace(
+            page_size=ps, tile=64, block_table=table, max_pages=pages_per_seq, seg_q_start=ar,
+            seg_pos0=torch.full((B,), args.ctx - 1, dtype=torch.int32, device="cuda"),
+            seg_kv_len=torch.full((B,), args.ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B],
+            prefill_tiles=None, num_decode=B, num_prefill_tiles=0, max_kv_len=args.ctx, num_tokens=B)
+        q = torch.randn(B, H * D, device="cuda", dtype=torch.bfloat16)
+        for label, flag in (("tensor-core", True), ("generic", False)):
+            ops.fast_attention = flag
+            us = timed(lambda i: ops.paged_attention(q, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D,
+                                                     D ** -0.5, None), args.iters)
+            gbs = B * args.ctx * KV * D * 4 / us / 1e3
+            print(f"decode attention B={B:<3d} ctx={args.ctx} heads {H}/{KV} D={D} {label:12s} {us:9.2f} us "
+                  f"{gbs:8.1f} GB/s {100 * gbs / peak:5.1f} % of peak", flush=True)
+        ops.fast_attention = True
+        del kv
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("what", choices=["gemm", "attention"])
+    ap.add_argument("--size", default="4b", choices=sorted(SIZES))
+    ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
+    ap.add_argument("--batch", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--rotate-mb", type=int, default=512, help="rotate through at least this many MB of operands")
+    args = ap.parse_args(argv)
+    from ..ops import get_ops
+    ops = get_ops("cuda:0")
+    peak, src = peak_gbs()
+    print(f"# peak {peak} GB/s ({src})")
+    (bench_gemm if args.what == "gemm" else bench_attention)(args, ops, peak)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

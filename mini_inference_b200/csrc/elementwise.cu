@@ -70,11 +70,74 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delt
     }
 }
 
+// Same arithmetic with 16-byte loads and the row held in registers between the two phases
+// (hidden a multiple of the vector width, at most NT * VPT vectors).
+template <typename T> __device__ __forceinline__ void store16(T* p, const float* v) {
+    if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint4 raw;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+}
+
+template <typename T, typename WT, int NT, int VPT>
+__global__ void __launch_bounds__(NT)
+add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
+                       const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    constexpr int V = Vec16<T>::N;
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const int nvec = hidden / V;
+    float vals[VPT][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * NT;
+        if (i < nvec) {
+            load16(x + src + (size_t)i * V, vals[k]);
+            if (delta) {
+                float d[V];
+                load16(delta + src + (size_t)i * V, d);
+#pragma unroll
+                for (int e = 0; e < V; ++e) vals[k][e] = round_to<T>(vals[k][e] + d[e]);
+                if (!rows) store16(x + src + (size_t)i * V, vals[k]);
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss += vals[k][e] * vals[k][e];
+        }
+    }
+    const float rstd = rsqrtf(block_sum<NT>(ss, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * NT;
+        if (i < nvec) {
+            float o[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) o[e] = round_to<T>(vals[k][e] * rstd) * to_f32(w[(size_t)i * V + e]);
+            store16(y + (size_t)r * hidden + (size_t)i * V, o);
+        }
+    }
+}
+
 MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
                              int hidden, float eps, int dtype, int w_dtype, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     constexpr int NT = 256;
-#define LAUNCH(T, WT) add_rmsnorm_kernel<T, WT, NT><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps)
+    const int vw = dtype == MI_BF16 ? 8 : 4;
+    const bool vec = hidden % vw == 0 && hidden / vw <= NT * (dtype == MI_BF16 ? 4 : 8) &&
+                     ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+#define LAUNCH(T, WT) do { \
+        if (vec) add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
+        else add_rmsnorm_kernel<T, WT, NT><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
+    } while (0)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);
     else if (w_dtype == MI_F32) LAUNCH(float, float);

@@ -5,9 +5,9 @@
 // engine/core/kv_cache.py:378-382 (the write, before attention).  The reference runs this
 // as ~15 elementwise kernels and two index copies.
 //
-// One block per token; the block first computes cos/sin of pos * inv_freq[i] in float32 once
-// (shared by all heads), then each warp takes heads in turn.  q is rotated in place inside
-// the qkv buffer; k (rotated) and v go to cache position `slot` of their kv head:
+// One warp per (token, head); a block holds 4 consecutive heads of one token.  Each lane computes
+// cos/sin of pos * inv_freq[i] in float32 for the pairs (i, i + D/2) it rotates.  q is rotated in
+// place inside the qkv buffer; k (rotated) and v go to cache position `slot` of their kv head:
 //   cache[(page * KV + head) * page_size + offset][0..D)   with page = slot / page_size.
 #include "common.cuh"
 
@@ -20,58 +20,55 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restr
                                           const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                           int H, int KV, int D, int page_size, float eps) {
-    __shared__ float cs[MAX_HALF], sn[MAX_HALF];
     const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= H + 2 * KV) return;
     const int half = D / 2;
-    if (inv_freq) {
-        const float pos = (float)positions[t];
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            float s, c;
-            sincosf(pos * inv_freq[i], &s, &c);
-            cs[i] = c; sn[i] = s;
-        }
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    T* row = qkv + (size_t)t * (H + 2 * KV) * D;
+    // heads 0..H-1 are q, H..H+KV-1 are k, H+KV..H+2KV-1 are v
+    T* x = qkv + ((size_t)t * (H + 2 * KV) + h) * D;
     size_t cache_base = 0;
-    if (k_cache) {
+    if (k_cache && h >= H) {
         const int slot = slots[t];
         cache_base = ((size_t)(slot / page_size) * KV * page_size + (slot % page_size)) * D;
     }
-    // heads 0..H-1 are q, H..H+KV-1 are k, H+KV..H+2KV-1 are v
-    for (int h = warp; h < H + 2 * KV; h += nwarps) {
-        T* x = row + (size_t)h * D;
-        if (h >= H + KV) {                                 // v: copy to the cache as it is
-            if (v_cache) {
-                T* dst = v_cache + cache_base + (size_t)(h - H - KV) * page_size * D;
+    if (h >= H + KV) {                                     // v: copy to the cache as it is
+        if (v_cache) {
+            T* dst = v_cache + cache_base + (size_t)(h - H - KV) * page_size * D;
+            constexpr int V = Vec16<T>::N;
+            if (D % V == 0) {
+                for (int i = lane; i < D / V; i += 32)
+                    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(x)[i];
+            } else {
                 for (int i = lane; i < D; i += 32) dst[i] = x[i];
             }
-            continue;
         }
-        const bool is_k = h >= H;
-        if (is_k && !k_cache) continue;                    // reads another step's cache: k unused
-        const WT* w = is_k ? k_w : q_w;
-        float ss = 0.f;
-        for (int i = lane; i < D; i += 32) { const float v = to_f32(x[i]); ss += v * v; }
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / (float)D + eps);
-        T* dst = is_k ? k_cache + cache_base + (size_t)(h - H) * page_size * D : x;
-        for (int i = lane; i < half; i += 32) {
-            float a = to_f32(x[i]), b = to_f32(x[i + half]);
-            if (w) {
-                a = round_to<T>(round_to<T>(a * rstd) * to_f32(w[i]));
-                b = round_to<T>(round_to<T>(b * rstd) * to_f32(w[i + half]));
-            }
-            float o1 = a, o2 = b;
-            if (inv_freq) {
-                const float c = cs[i], s = sn[i];
-                o1 = a * c - b * s;
-                o2 = b * c + a * s;
-            }
-            dst[i] = from_f32<T>(o1);
-            dst[i + half] = from_f32<T>(o2);
+        return;
+    }
+    const bool is_k = h >= H;
+    if (is_k && !k_cache) return;                          // reads another step's cache: k unused
+    const WT* w = is_k ? k_w : q_w;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) { const float v = to_f32(x[i]); ss += v * v; }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float pos = inv_freq ? (float)positions[t] : 0.f;
+    T* dst = is_k ? k_cache + cache_base + (size_t)(h - H) * page_size * D : x;
+    for (int i = lane; i < half; i += 32) {
+        float a = to_f32(x[i]), b = to_f32(x[i + half]);
+        if (w) {
+            a = round_to<T>(round_to<T>(a * rstd) * to_f32(w[i]));
+            b = round_to<T>(round_to<T>(b * rstd) * to_f32(w[i + half]));
         }
+        float o1 = a, o2 = b;
+        if (inv_freq) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            o1 = a * cs - b * sn;
+            o2 = b * cs + a * sn;
+        }
+        dst[i] = from_f32<T>(o1);
+        dst[i + half] = from_f32<T>(o2);
     }
 }
 
@@ -81,7 +78,7 @@ MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w,
                                     cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (D % 2 || D / 2 > MAX_HALF) return -2;
-#define LAUNCH(T, WT) qk_norm_rope_cache_kernel<T, WT><<<T_, 128, 0, stream>>>((T*)qkv, (const WT*)q_w, (const WT*)k_w, \
+#define LAUNCH(T, WT) qk_norm_rope_cache_kernel<T, WT><<<dim3(T_, (H + 2 * KV + 3) / 4), 128, 0, stream>>>((T*)qkv, (const WT*)q_w, (const WT*)k_w, \
         inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, D, page_size, eps)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);

@@ -60,6 +60,7 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
+        self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
         self.launches = 0                    # kernels of this package launched so far
 
@@ -104,6 +105,18 @@ class CudaOps:
             _check(self.lib.mi_gemm_f32_nt(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, self._stream()), "gemm_f32")
             self.launches += 1
             return out
+        M, K = x.shape
+        if (self.skinny_gemm and M <= 64 and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            N = w.shape[0]
+            od = out_dtype or x.dtype
+            out = torch.empty((M, N), dtype=od, device=x.device)
+            err = self.lib.mi_gemm_skinny(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), self._stream())
+            if err == 0:
+                self.launches += 1
+                return out
+            if err != -2:
+                _check(err, "gemm_skinny")
         if out_dtype is not None and out_dtype != x.dtype:
             try:
                 return torch.mm(x, w.t(), out_dtype=out_dtype)
@@ -129,7 +142,8 @@ class CudaOps:
         request has 256-key pieces (kernels/paged_attention/decode_triton.py:114-120)."""
         if self.force_splits:
             return self.force_splits
-        return max(1, min(math.ceil(2 * self.NUM_SMS / ctas), math.ceil(max_kv_len / 256), 32))
+        slots = 2 * self.NUM_SMS                           # two blocks are resident per SM: stay within one wave
+        return max(1, min(slots // ctas, math.ceil(max_kv_len / 256), 32))
 
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
         T = q.shape[0]

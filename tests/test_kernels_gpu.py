@@ -95,6 +95,26 @@ def test_linear_bf16(ops, M, N, K):
     assert ((out - want).abs().max() / want.abs().max()).item() < 1e-4
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (6144, 2560), (100, 64), (517, 96), (19456, 2560), (2560, 9728)])
+def test_gemm_skinny(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :K]      # strided rows
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    before = ops.launches
+    got = ops.linear(x, w, out_dtype=torch.float32)
+    assert ops.launches == before + 1                     # the package's own kernel ran
+    want = x.double() @ w.double().T
+    assert ((got.double() - want).abs().max() / want.abs().max()).item() < 1e-5
+    got16 = ops.linear(x, w)
+    assert got16.dtype == torch.bfloat16
+    close(got16, want, torch.bfloat16)
+    # a token's result does not depend on the rest of the batch (same bits alone and in company)
+    assert torch.equal(ops.linear(x[:1], w, out_dtype=torch.float32), got[:1])
+    if M > 8:
+        assert torch.equal(ops.linear(x[5:9], w, out_dtype=torch.float32), got[5:9])
+
+
 def make_meta(page_size, segs, num_pages, seed, tile=64):
     """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
     shaped like engine.batch.GroupMeta."""
