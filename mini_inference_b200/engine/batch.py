@@ -73,7 +73,8 @@ class StepBatch:
         self.num_decode, self.num_prefill_tiles, self.num_logit_rows = len(decode), len(tiles), len(rows)
         self.host = {"seg_q_start": q_start, "seg_pos0": np.asarray(pos0, dtype=np.int32),
                      "seg_kv_len": np.asarray(kv_len, dtype=np.int32), "decode_segs": decode,
-                     "prefill_tiles": tiles, "positions": positions}
+                     "prefill_tiles": tiles, "positions": positions,
+                     "seg_slot": [e.seq.slot for e in entries]}
 
         parts = {
             "token_ids": ids.astype(np.int32), "positions": positions, "token_seg": token_seg,
