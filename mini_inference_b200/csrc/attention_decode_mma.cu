@@ -91,22 +91,25 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 kreg[nt][j] = *reinterpret_cast<const uint4*>(base + (size_t)(nt * 8 + g) * D + 32 * j + 8 * c);
     };
 
-    int blk = b0 + warp;
-    if (blk < b1) load_k(blk);
-    for (; blk < b1; blk += DEC_WARPS) {
-        // values of this block: rows of keys 2c, 2c+1, 2c+8, 2c+9, 16 bytes at d = 64 hb + 8 g
-        uint4 vreg[4][HALVES];
-        {
-            const int page = table_row[(blk * 16) / ps];
-            const __nv_bfloat16* base = v_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+    // values of a block: rows of keys 2c, 2c+1, 2c+8, 2c+9, 16 bytes at d = 64 hb + 8 g
+    uint4 vreg[4][HALVES];
+    auto load_v = [&](int blk) {
+        const int page = table_row[(blk * 16) / ps];
+        const __nv_bfloat16* base = v_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = 2 * c + (i & 1) + 8 * (i >> 1);
+        for (int i = 0; i < 4; ++i) {
+            const int key = 2 * c + (i & 1) + 8 * (i >> 1);
 #pragma unroll
-                for (int hb = 0; hb < HALVES; ++hb)
-                    vreg[i][hb] = *reinterpret_cast<const uint4*>(base + (size_t)key * D + 64 * hb + 8 * g);
-            }
+            for (int hb = 0; hb < HALVES; ++hb)
+                vreg[i][hb] = *reinterpret_cast<const uint4*>(base + (size_t)key * D + 64 * hb + 8 * g);
         }
+    };
+
+    // Software pipeline: the keys of block i+1 are requested right after the scores of block i,
+    // the values of block i+1 right after block i's P*V, so each load has a whole iteration to land.
+    int blk = b0 + warp;
+    if (blk < b1) { load_k(blk); load_v(blk); }
+    for (; blk < b1; blk += DEC_WARPS) {
         // scores: 16 (heads) x 16 (keys) as two 8-key tiles
         float sc[2][4];
 #pragma unroll
@@ -168,6 +171,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 mma_bf16_16816(acc, pa, vb0, vb1);
             }
         }
+        if (blk + DEC_WARPS < b1) load_v(blk + DEC_WARPS);
     }
 
     // row sums over the quad, then merge the warps

@@ -51,7 +51,7 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, 3)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
@@ -62,12 +62,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     constexpr int DT = D / 8;               // 8-column output tiles
     constexpr int TILE_BYTES = BK * D * 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    const uint32_t sK = sQ + BQ * D * 2, sV = sK + 2 * TILE_BYTES;
+    const uint32_t sK = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sV = sK + 2 * TILE_BYTES;
+    const uint32_t sQ = sK + TILE_BYTES;           // the query tile borrows the second key buffer until it is in registers
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int seg = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
+    const int tile = gridDim.x - 1 - blockIdx.x;   // later tiles see more keys: start them first
+    const int seg = tiles[2 * tile], r0 = tiles[2 * tile + 1];
     const int h = blockIdx.y, kvh = h / (H / KV);
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
     const int rows = min(BQ, n - r0);
@@ -106,18 +108,18 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int p_row0 = pos0 + r0 + warp * 16 + g, p_row1 = p_row0 + 8;     // positions of this thread's two rows
 
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const int mi = lane >> 3;
+        ldmatrix_x4(qa[ks], sQ + swz<D>(warp * 16 + (lane & 7) + (mi & 1) * 8, ks * 2 + (mi >> 1)));
+    }
+    __syncthreads();                               // the borrowed buffer is free again
+
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
-        if (kt < kt_hi) { load_kv(kt + 1, buf ^ 1); cp_async_commit(); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
-        __syncthreads();
-        if (kt == kt_lo) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                const int mi = lane >> 3;
-                ldmatrix_x4(qa[ks], sQ + swz<D>(warp * 16 + (lane & 7) + (mi & 1) * 8, ks * 2 + (mi >> 1)));
-            }
-        }
+        if (kt < kt_hi) { load_kv(kt + 1, buf ^ 1); cp_async_commit(); }      // lands while this tile is computed
         const uint32_t kbuf = sK + buf * TILE_BYTES, vbuf = sV + buf * TILE_BYTES;
         // ---- S = Q K^T : 16 rows x 64 keys per warp
         float s[BK / 8][4];
@@ -133,20 +135,31 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 mma16816(s[2 * np], qa[ks], b[0], b[1]);
                 mma16816(s[2 * np + 1], qa[ks], b[2], b[3]);
             }
-        // ---- mask + online softmax (base 2)
+        // ---- mask + online softmax (base 2); a tile wholly inside every row's visible range needs no mask
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool inside = kt * BK + BK - 1 <= p_row0 - g && (window <= 0 || kt * BK > p_row0 - g + 15 - window);
+        if (inside) {
 #pragma unroll
-        for (int nt = 0; nt < BK / 8; ++nt)
+            for (int nt = 0; nt < BK / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = kt * BK + nt * 8 + 2 * c + e;
-                const bool ok0 = j <= p_row0 && (window <= 0 || j > p_row0 - window);
-                const bool ok1 = j <= p_row1 && (window <= 0 || j > p_row1 - window);
-                s[nt][e] = ok0 ? s[nt][e] * scale_log2 : -INFINITY;
-                s[nt][2 + e] = ok1 ? s[nt][2 + e] * scale_log2 : -INFINITY;
-                mx0 = fmaxf(mx0, s[nt][e]);
-                mx1 = fmaxf(mx1, s[nt][2 + e]);
+                for (int e = 0; e < 4; ++e) s[nt][e] *= scale_log2;
+                mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
             }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = kt * BK + nt * 8 + 2 * c + e;
+                    const bool ok0 = j <= p_row0 && (window <= 0 || j > p_row0 - window);
+                    const bool ok1 = j <= p_row1 && (window <= 0 || j > p_row1 - window);
+                    s[nt][e] = ok0 ? s[nt][e] * scale_log2 : -INFINITY;
+                    s[nt][2 + e] = ok1 ? s[nt][2 + e] * scale_log2 : -INFINITY;
+                    mx0 = fmaxf(mx0, s[nt][e]);
+                    mx1 = fmaxf(mx1, s[nt][2 + e]);
+                }
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
@@ -178,7 +191,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 mma16816(o[2 * dp + 1], pa, b[2], b[3]);
             }
         }
-        __syncthreads();                       // everyone is done with this buffer before it is refilled
+        cp_async_wait<0>();
+        __syncthreads();                       // the next tile has landed and everyone is done with this one
     }
 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -203,7 +217,7 @@ MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cac
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
-    const size_t smem = (size_t)(BQ + 4 * BK) * D * 2;
+    const size_t smem = (size_t)4 * BK * D * 2;
     dim3 grid(num_tiles, H);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD, IDX) do { \

@@ -66,4 +66,23 @@ template <typename T> __device__ __forceinline__ void load16(const T* p, float* 
     }
 }
 
+// two neighbouring elements in one access (p must be aligned to 2 elements)
+template <typename T> __device__ __forceinline__ void load2(const T* p, float& a, float& b) {
+    if constexpr (sizeof(T) == 4) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        a = v.x; b = v.y;
+    } else {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+        a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
+    }
+}
+template <typename T> __device__ __forceinline__ void store2(T* p, float a, float b) {
+    if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float2*>(p) = make_float2(a, b);
+    } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+
 }  // namespace mi

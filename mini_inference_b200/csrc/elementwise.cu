@@ -158,13 +158,35 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     }
 }
 
+// 16 bytes of gate, 16 bytes of up and 16 bytes of output per thread (inter a multiple of the vector width)
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    constexpr int V = Vec16<T>::N;
+    const int vec_per_row = inter / V;
+    const size_t n = (size_t)rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / vec_per_row, c = (i % vec_per_row) * V;
+        float g[V], u[V], o[V];
+        load16(gate_up + r * 2 * inter + c, g);
+        load16(gate_up + r * 2 * inter + inter + c, u);
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+        store16(out + r * inter + c, o);
+    }
+}
+
 MI_EXPORT int mi_swiglu(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
     const size_t n = (size_t)rows * inter;
     if (n == 0) return 0;
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    if (dtype == MI_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter);
-    else
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, inter);
+    const int vw = dtype == MI_BF16 ? 8 : 4;
+    const bool vec = inter % vw == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const size_t work = vec ? n / vw : n;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+#define LAUNCH(T) do { \
+        if (vec) swiglu_vec_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, rows, inter); \
+        else swiglu_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, rows, inter); \
+    } while (0)
+    if (dtype == MI_BF16) LAUNCH(__nv_bfloat16); else LAUNCH(float);
+#undef LAUNCH
     return (int)cudaGetLastError();
 }

@@ -1,0 +1,297 @@
+// Persistent weight-streaming GEMM for decode steps: out[M, N] = X[M, K] * W[N, K]^T, M <= 32,
+// bfloat16 in, float32 accumulation.  TMA + mbarrier pipeline, stream-K work split.
+//
+// Reference (davidjoyme/mini-inference engine/core/fused_linear.py:29-34): the library GEMM; its
+// own measurements (README.md:29, results/micro/gemm_qwen3.json) put the skinny decode products
+// at 17-83 % of peak bandwidth, worst for the narrow ones (o, down) where few tiles exist and
+// whole waves of blocks go idle.  This kernel is organised around the one thing that matters at
+// these shapes, keeping every SM's HBM pipe full for the whole call:
+//   * one persistent block per SM; a producer thread streams [128 rows x 64 k] weight boxes
+//     with TMA (cp.async.bulk.tensor, 128-byte swizzle) into an 8-stage ring (128 KB in flight
+//     per SM), signalled by mbarriers; 8 consumer warps turn each box into mma.sync work
+//     ("swap-AB": weight rows are the 16-row side, tokens the 8-wide side);
+//   * stream-K: the (row tile, k chunk) units of the whole matrix are cut into equal contiguous
+//     shares, one per block, whatever N and K are, so no SM waits for a straggler; a row tile
+//     cut between blocks is finished by whichever block arrives last, which adds the partial
+//     sums in the fixed order of the shares (not of arrival).  The split depends on (N, K, grid)
+//     only, never on M, so a token's result does not depend on its company in the batch.
+// Every wait on an mbarrier is bounded; a wait that runs out raises an error word and the block
+// leaves.  No cluster multicast is used.
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+using namespace mi;
+
+namespace {
+
+constexpr int TR = 128;                 // weight rows per tile
+constexpr int KC = 64;                  // k per stage (128 bytes: one swizzle row)
+constexpr int NS = 8;                   // ring stages
+constexpr int STAGE_BYTES = TR * KC * 2;
+constexpr int CONSUMERS = 8;            // consumer warps, 16 rows each
+constexpr int THREADS = 32 * (1 + CONSUMERS);
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the barrier did not flip within the limit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(40);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 :: "r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(CONSUMERS * 32) : "memory"); }
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename OutT> __device__ __forceinline__ OutT cvt_out(float v);
+template <> __device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// block that owns unit u when U units are cut into G contiguous shares [floor(U b / G), floor(U (b+1) / G))
+__device__ __forceinline__ int owner_of(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
+
+template <int NT, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16* __restrict__ X, int ldx,
+                   OutT* __restrict__ out, int ldo, int M, int N, int K, float* __restrict__ workspace, int max_contrib,
+                   int* __restrict__ counters, int* __restrict__ error_word) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + NS * STAGE_BYTES);
+    __shared__ int last_flag;
+    const uint32_t stage0 = smem_u32(base), full0 = smem_u32(bars), empty0 = smem_u32(bars + NS);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONSUMERS); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    const int NKC = K / KC, NRT = (N + TR - 1) / TR;
+    const long long U = (long long)NRT * NKC, G = gridDim.x;
+    const long long u0 = U * blockIdx.x / G, u1 = U * (blockIdx.x + 1) / G;
+
+    if (warp == 0) {
+        // ---------------- producer: one thread keeps the ring full
+        if (lane == 0) {
+            for (long long u = u0; u < u1; ++u) {
+                const int i = (int)(u - u0), s = i % NS;
+                if (i >= NS && !mbar_wait(empty0 + 8 * s, ((i / NS) - 1) & 1)) { atomicExch(error_word, 1); break; }
+                const int rt = (int)(u / NKC), kc = (int)(u % NKC);
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(stage0 + s * STAGE_BYTES, &wmap, kc * KC, rt * TR, full0 + 8 * s);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: warp cw owns rows cw*16 .. cw*16+15 of every tile
+    const int cw = warp - 1, g = lane >> 2, c = lane & 3;
+    const int ctid = threadIdx.x - 32;
+    constexpr int TOK = NT * 8;
+    const __nv_bfloat16* xrow[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        xok[nt] = nt * 8 + g < M;
+        xrow[nt] = X + (size_t)(xok[nt] ? nt * 8 + g : 0) * ldx + 8 * c;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    const int r_lo = cw * 16 + g, r_hi = r_lo + 8;
+    int seg_start_kc = (int)(u0 % NKC);
+
+    for (long long u = u0; u < u1; ++u) {
+        const int i = (int)(u - u0), s = i % NS;
+        const int rt = (int)(u / NKC), kc = (int)(u % NKC);
+        if (!mbar_wait(full0 + 8 * s, (i / NS) & 1)) { atomicExch(error_word, 2); return; }
+        const unsigned char* st = base + s * STAGE_BYTES;
+#pragma unroll
+        for (int win = 0; win < 2; ++win) {
+            const int ch = win * 4 + c;
+            const uint4 a_lo = *reinterpret_cast<const uint4*>(st + r_lo * 128 + ((ch ^ (r_lo & 7)) << 4));
+            const uint4 a_hi = *reinterpret_cast<const uint4*>(st + r_hi * 128 + ((ch ^ (r_hi & 7)) << 4));
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                uint4 b = make_uint4(0, 0, 0, 0);
+                if (xok[nt]) b = __ldg(reinterpret_cast<const uint4*>(xrow[nt] + (size_t)kc * KC + win * 32));
+                mma16816(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+                mma16816(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+
+        if (kc != NKC - 1 && u != u1 - 1) continue;
+        // ---------------- this block's share of row tile rt ends here
+        const bool whole = seg_start_kc == 0 && kc == NKC - 1;
+        if (whole) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int t = nt * 8 + 2 * c, n_lo = rt * TR + r_lo, n_hi = rt * TR + r_hi;
+                if (t < M) {
+                    if (n_lo < N) out[(size_t)t * ldo + n_lo] = cvt_out<OutT>(acc[nt][0]);
+                    if (n_hi < N) out[(size_t)t * ldo + n_hi] = cvt_out<OutT>(acc[nt][2]);
+                }
+                if (t + 1 < M) {
+                    if (n_lo < N) out[(size_t)(t + 1) * ldo + n_lo] = cvt_out<OutT>(acc[nt][1]);
+                    if (n_hi < N) out[(size_t)(t + 1) * ldo + n_hi] = cvt_out<OutT>(acc[nt][3]);
+                }
+            }
+        } else {
+            const long long first_unit = (long long)rt * NKC;
+            const int first = owner_of(first_unit, U, G), last = owner_of(first_unit + NKC - 1, U, G);
+            const int slot = (int)blockIdx.x - first, contrib = last - first + 1;
+            float* mine = workspace + ((size_t)rt * max_contrib + slot) * TR * TOK;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int t = nt * 8 + 2 * c;
+                mine[r_lo * TOK + t] = acc[nt][0]; mine[r_lo * TOK + t + 1] = acc[nt][1];
+                mine[r_hi * TOK + t] = acc[nt][2]; mine[r_hi * TOK + t + 1] = acc[nt][3];
+            }
+            __threadfence();
+            consumer_sync();
+            if (ctid == 0) last_flag = atomicAdd(&counters[rt], 1) == contrib - 1;
+            consumer_sync();
+            if (last_flag) {                                   // every other share of this tile is in the workspace
+                __threadfence();
+                const float* tile_ws = workspace + (size_t)rt * max_contrib * TR * TOK;
+                for (int idx = ctid; idx < TR * TOK; idx += CONSUMERS * 32) {
+                    const int t = idx / TR, r = idx % TR;
+                    if (t < M && rt * TR + r < N) {
+                        float sum = 0.f;
+                        for (int k = 0; k < contrib; ++k) sum += __ldcg(tile_ws + ((size_t)k * TR + r) * TOK + t);
+                        out[(size_t)t * ldo + rt * TR + r] = cvt_out<OutT>(sum);
+                    }
+                }
+                if (ctid == 0) counters[rt] = 0;               // ready for the next call
+            }
+            consumer_sync();
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+        seg_start_kc = 0;
+    }
+}
+
+// ---------------------------------------------------------------- host side
+PFN_cuTensorMapEncodeTiled encode_fn = nullptr;
+std::mutex host_mutex;
+std::map<std::tuple<const void*, int, int>, CUtensorMap> weight_maps;
+int sm_count = 0;
+
+int get_weight_map(const void* W, int N, int K, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(host_mutex);
+    if (!encode_fn) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return -4;
+        encode_fn = (PFN_cuTensorMapEncodeTiled)fn;
+    }
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    auto key = std::make_tuple(W, N, K);
+    auto it = weight_maps.find(key);
+    if (it == weight_maps.end()) {
+        CUtensorMap m;
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        const cuuint32_t box[2] = {KC, TR};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode_fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(W), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return -5;
+        it = weight_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int NT, typename OutT>
+int launch(const CUtensorMap& map, const void* X, int ldx, void* out, int ldo, int M, int N, int K, float* workspace,
+           int max_contrib, int* counters, int* error_word, int grid, cudaStream_t stream) {
+    const size_t smem = (size_t)NS * STAGE_BYTES + 2 * NS * 8 + 1024;
+    auto kern = gemm_stream_kernel<NT, OutT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<grid, THREADS, smem, stream>>>(map, (const __nv_bfloat16*)X, ldx, (OutT*)out, ldo, M, N, K, workspace,
+                                          max_contrib, counters, error_word);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Work-split facts the caller needs to size the scratch: grid (blocks), row tiles, and the most
+// blocks that can share one row tile.  Returns -2 when the shape is not taken (K % 64, M > 32).
+MI_EXPORT int mi_gemm_stream_plan(int M, int N, int K, int* grid, int* row_tiles, int* max_contrib) {
+    if (M < 1 || M > 32 || K % KC || K < KC || N < 1) return -2;
+    if (!sm_count) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return -4;
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long long NKC = K / KC, NRT = (N + TR - 1) / TR, U = NRT * NKC;
+    const long long G = U < sm_count ? U : sm_count;
+    const long long share = U / G;                       // smallest share
+    *grid = (int)G;
+    *row_tiles = (int)NRT;
+    *max_contrib = (int)((NKC + share - 1) / share + 1);
+    return 0;
+}
+
+// workspace: float32 [row_tiles * max_contrib * 128 * tokens_padded] with tokens_padded = 8, 16 or 32 for
+// M <= 8, 16, 32; counters: int32 [row_tiles], zero before the first call (the kernel leaves them zero);
+// error_word: int32, set non-zero if a bounded wait inside the kernel ran out.
+MI_EXPORT int mi_gemm_stream(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K,
+                             int out_dtype, float* workspace, int* counters, int* error_word, cudaStream_t stream) {
+    int grid, row_tiles, max_contrib;
+    int rc = mi_gemm_stream_plan(M, N, K, &grid, &row_tiles, &max_contrib);
+    if (rc) return rc;
+    if (ldx % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16) || (K * 2) % 16) return -2;
+    CUtensorMap map;
+    rc = get_weight_map(W, N, K, &map);
+    if (rc) return rc;
+#define GO(NT, OT) launch<NT, OT>(map, X, ldx, out, ldo, M, N, K, workspace, max_contrib, counters, error_word, grid, stream)
+    if (out_dtype == MI_F32) return M <= 8 ? GO(1, float) : M <= 16 ? GO(2, float) : GO(4, float);
+    return M <= 8 ? GO(1, __nv_bfloat16) : M <= 16 ? GO(2, __nv_bfloat16) : GO(4, __nv_bfloat16);
+#undef GO
+}

@@ -48,27 +48,38 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restr
     const bool is_k = h >= H;
     if (is_k && !k_cache) return;                          // reads another step's cache: k unused
     const WT* w = is_k ? k_w : q_w;
+    // each lane takes PAIRS of neighbouring elements (one 4- or 8-byte access) of both halves
     float ss = 0.f;
-    for (int i = lane; i < D; i += 32) { const float v = to_f32(x[i]); ss += v * v; }
+    for (int i = 2 * lane; i < half; i += 64) {
+        float a0, a1, b0, b1;
+        load2(x + i, a0, a1);
+        load2(x + i + half, b0, b1);
+        ss += a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1;
+    }
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / (float)D + eps);
     const float pos = inv_freq ? (float)positions[t] : 0.f;
     T* dst = is_k ? k_cache + cache_base + (size_t)(h - H) * page_size * D : x;
-    for (int i = lane; i < half; i += 32) {
-        float a = to_f32(x[i]), b = to_f32(x[i + half]);
-        if (w) {
-            a = round_to<T>(round_to<T>(a * rstd) * to_f32(w[i]));
-            b = round_to<T>(round_to<T>(b * rstd) * to_f32(w[i + half]));
+    for (int i = 2 * lane; i < half; i += 64) {
+        float a[2], b[2], o1[2], o2[2];
+        load2(x + i, a[0], a[1]);
+        load2(x + i + half, b[0], b[1]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (w) {
+                a[e] = round_to<T>(round_to<T>(a[e] * rstd) * to_f32(w[i + e]));
+                b[e] = round_to<T>(round_to<T>(b[e] * rstd) * to_f32(w[i + e + half]));
+            }
+            o1[e] = a[e]; o2[e] = b[e];
+            if (inv_freq) {
+                float sn, cs;
+                sincosf(pos * inv_freq[i + e], &sn, &cs);
+                o1[e] = a[e] * cs - b[e] * sn;
+                o2[e] = b[e] * cs + a[e] * sn;
+            }
         }
-        float o1 = a, o2 = b;
-        if (inv_freq) {
-            float sn, cs;
-            sincosf(pos * inv_freq[i], &sn, &cs);
-            o1 = a * cs - b * sn;
-            o2 = b * cs + a * sn;
-        }
-        dst[i] = from_f32<T>(o1);
-        dst[i + half] = from_f32<T>(o2);
+        store2(dst + i, o1[0], o1[1]);
+        store2(dst + i + half, o2[0], o2[1]);
     }
 }
 
@@ -77,7 +88,7 @@ MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w,
                                     int T_, int H, int KV, int D, int page_size, float eps, int dtype, int w_dtype,
                                     cudaStream_t stream) {
     if (T_ == 0) return 0;
-    if (D % 2 || D / 2 > MAX_HALF) return -2;
+    if (D % 4 || D / 2 > MAX_HALF) return -2;
 #define LAUNCH(T, WT) qk_norm_rope_cache_kernel<T, WT><<<dim3(T_, (H + 2 * KV + 3) / 4), 128, 0, stream>>>((T*)qkv, (const WT*)q_w, (const WT*)k_w, \
         inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, D, page_size, eps)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

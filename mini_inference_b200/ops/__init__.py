@@ -60,7 +60,8 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
-        self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel
+        self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
+        self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
         self.launches = 0                    # kernels of this package launched so far
 
@@ -106,7 +107,7 @@ class CudaOps:
             self.launches += 1
             return out
         M, K = x.shape
-        if (self.skinny_gemm and M <= 64 and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+        if (self.skinny_gemm and M <= self.skinny_max_rows and w.shape[0] <= self.skinny_max_cols and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             N = w.shape[0]
             od = out_dtype or x.dtype
