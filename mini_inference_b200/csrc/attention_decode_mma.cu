@@ -49,6 +49,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
     extern __shared__ float smem[];     // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int G = H / KV;
@@ -226,7 +228,7 @@ MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cach
     const size_t smem = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD) do { \
-        attn_decode_mma_kernel<DD><<<grid, DEC_WARPS * 32, smem, stream>>>( \
+        return (int)launch_pdl(attn_decode_mma_kernel<DD>, grid, dim3(DEC_WARPS * 32), smem, stream, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
             H, KV, ps, scale_log2, window); } while (0)

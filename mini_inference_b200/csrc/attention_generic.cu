@@ -150,6 +150,8 @@ template <typename T>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part,
                                          T* __restrict__ out, const int* __restrict__ decode_segs,
                                          const int* __restrict__ seg_q_start, int H, int D, int S) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x, h = blockIdx.y;
     const int tok = seg_q_start[decode_segs[i]];
     const size_t base = ((size_t)i * H + h) * S;
@@ -211,8 +213,6 @@ MI_EXPORT int mi_attn_decode_merge(const float* o_part, const float* lse_part, v
     if (num_decode == 0) return 0;
     dim3 mgrid(num_decode, H);
     if (dtype == MI_BF16)
-        attn_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, H, D, splits);
-    else
-        attn_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, D, splits);
-    return (int)cudaGetLastError();
+        return (int)launch_pdl(attn_decode_merge_kernel<__nv_bfloat16>, mgrid, dim3(128), 0, stream, o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, H, D, splits);
+    return (int)launch_pdl(attn_decode_merge_kernel<float>, mgrid, dim3(128), 0, stream, o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, D, splits);
 }

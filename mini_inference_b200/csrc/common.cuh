@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <cstdlib>
 
 #define MI_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -11,6 +12,14 @@
 #define MI_BF16 1
 
 namespace mi {
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs; pdl_wait() blocks until the
+// predecessor has completed and its writes are visible, so it must come before the first access to
+// anything the predecessor produces (or still reads).  pdl_trigger() lets the NEXT kernel start
+// its own preamble early.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -85,4 +94,22 @@ template <typename T> __device__ __forceinline__ void store2(T* p, float a, floa
     }
 }
 
+}  // namespace mi
+
+// Host side: launch with the programmatic-serialization attribute when mi_pdl_enabled() says so.
+namespace mi {
+inline bool pdl_enabled() {
+    static const bool on = [] { const char* e = std::getenv("MI_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace mi

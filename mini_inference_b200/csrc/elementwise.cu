@@ -12,6 +12,8 @@ using namespace mi;
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;       // the host refuses such ids; never read out of range
@@ -31,10 +33,8 @@ MI_EXPORT int mi_embedding(const int* ids, const void* table, void* out, int T_,
                            int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (dtype == MI_BF16)
-        embedding_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, hidden, vocab);
-    else
-        embedding_kernel<float><<<T_, 128, 0, stream>>>(ids, (const float*)table, (float*)out, hidden, vocab);
-    return (int)cudaGetLastError();
+        return (int)launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(T_), dim3(128), 0, stream, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, hidden, vocab);
+    return (int)launch_pdl(embedding_kernel<float>, dim3(T_), dim3(128), 0, stream, ids, (const float*)table, (float*)out, hidden, vocab);
 }
 
 // ------------------------------------------------------------------ (x += delta); y = rmsnorm(x) * w
@@ -46,6 +46,8 @@ template <typename T, typename WT, int NT>
 __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w,
                                    T* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     T* xr = x + src;
@@ -93,6 +95,8 @@ add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT*
                        const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[32];
     constexpr int V = Vec16<T>::N;
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const int nvec = hidden / V;
@@ -135,8 +139,8 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
     const bool vec = hidden % vw == 0 && hidden / vw <= NT * (dtype == MI_BF16 ? 4 : 8) &&
                      ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)delta % 16 == 0);
 #define LAUNCH(T, WT) do { \
-        if (vec) add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
-        else add_rmsnorm_kernel<T, WT, NT><<<num_rows, NT, 0, stream>>>((T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
+        if (vec) return (int)launch_pdl(add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
+        return (int)launch_pdl(add_rmsnorm_kernel<T, WT, NT>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
     } while (0)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);
@@ -149,6 +153,8 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
 // ------------------------------------------------------------------ silu(gate) * up
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    pdl_trigger();
+    pdl_wait();
     const size_t n = (size_t)rows * inter;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / inter, c = i % inter;
@@ -162,6 +168,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
     constexpr int V = Vec16<T>::N;
+    pdl_trigger();
+    pdl_wait();
     const int vec_per_row = inter / V;
     const size_t n = (size_t)rows * vec_per_row;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -183,8 +191,8 @@ MI_EXPORT int mi_swiglu(const void* gate_up, void* out, int rows, int inter, int
     const size_t work = vec ? n / vw : n;
     const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
 #define LAUNCH(T) do { \
-        if (vec) swiglu_vec_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, rows, inter); \
-        else swiglu_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, rows, inter); \
+        if (vec) return (int)launch_pdl(swiglu_vec_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, rows, inter); \
+        return (int)launch_pdl(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, rows, inter); \
     } while (0)
     if (dtype == MI_BF16) LAUNCH(__nv_bfloat16); else LAUNCH(float);
 #undef LAUNCH

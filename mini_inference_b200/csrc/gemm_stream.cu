@@ -80,12 +80,15 @@ __device__ __forceinline__ int owner_of(long long u, long long U, long long G) {
 
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16* __restrict__ X, int ldx,
+gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    OutT* __restrict__ out, int ldo, int M, int N, int K, float* __restrict__ workspace, int max_contrib,
                    int* __restrict__ counters, int* __restrict__ error_word) {
+    constexpr int TOK = NT * 8;
+    constexpr int X_BYTES = TOK * KC * 2;                  // the tokens' slice of the same k chunk
+    constexpr int STAGE = STAGE_BYTES + X_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + NS * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + NS * STAGE);
     __shared__ int last_flag;
     const uint32_t stage0 = smem_u32(base), full0 = smem_u32(bars), empty0 = smem_u32(bars + NS);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -96,20 +99,33 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     __syncthreads();
+    pdl_trigger();                                         // the next kernel may begin its own preamble
 
     const int NKC = K / KC, NRT = (N + TR - 1) / TR;
     const long long U = (long long)NRT * NKC, G = gridDim.x;
     const long long u0 = U * blockIdx.x / G, u1 = U * (blockIdx.x + 1) / G;
 
     if (warp == 0) {
-        // ---------------- producer: one thread keeps the ring full
+        // ---------------- producer: one thread keeps the ring full.  Weights do not depend on the
+        // kernel before this one, so the first ring-full of weight boxes is requested BEFORE waiting
+        // for it; the activations of those stages follow once it has finished.
         if (lane == 0) {
-            for (long long u = u0; u < u1; ++u) {
+            const int ahead = (int)((u1 - u0) < NS ? (u1 - u0) : NS);
+            for (int i = 0; i < ahead; ++i) {
+                const long long u = u0 + i;
+                mbar_expect_tx(full0 + 8 * i, STAGE);
+                tma_load_2d(stage0 + i * STAGE, &wmap, (int)(u % NKC) * KC, (int)(u / NKC) * TR, full0 + 8 * i);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(stage0 + i * STAGE + STAGE_BYTES, &xmap, (int)((u0 + i) % NKC) * KC, 0, full0 + 8 * i);
+            for (long long u = u0 + ahead; u < u1; ++u) {
                 const int i = (int)(u - u0), s = i % NS;
-                if (i >= NS && !mbar_wait(empty0 + 8 * s, ((i / NS) - 1) & 1)) { atomicExch(error_word, 1); break; }
+                if (!mbar_wait(empty0 + 8 * s, ((i / NS) - 1) & 1)) { atomicExch(error_word, 1); break; }
                 const int rt = (int)(u / NKC), kc = (int)(u % NKC);
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                tma_load_2d(stage0 + s * STAGE_BYTES, &wmap, kc * KC, rt * TR, full0 + 8 * s);
+                mbar_expect_tx(full0 + 8 * s, STAGE);
+                tma_load_2d(stage0 + s * STAGE, &wmap, kc * KC, rt * TR, full0 + 8 * s);
+                tma_load_2d(stage0 + s * STAGE + STAGE_BYTES, &xmap, kc * KC, 0, full0 + 8 * s);
             }
         }
         return;
@@ -118,14 +134,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16
     // ---------------- consumers: warp cw owns rows cw*16 .. cw*16+15 of every tile
     const int cw = warp - 1, g = lane >> 2, c = lane & 3;
     const int ctid = threadIdx.x - 32;
-    constexpr int TOK = NT * 8;
-    const __nv_bfloat16* xrow[NT];
-    bool xok[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        xok[nt] = nt * 8 + g < M;
-        xrow[nt] = X + (size_t)(xok[nt] ? nt * 8 + g : 0) * ldx + 8 * c;
-    }
+    pdl_wait();                                            // before the first write to out / workspace
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
@@ -136,7 +145,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16
         const int i = (int)(u - u0), s = i % NS;
         const int rt = (int)(u / NKC), kc = (int)(u % NKC);
         if (!mbar_wait(full0 + 8 * s, (i / NS) & 1)) { atomicExch(error_word, 2); return; }
-        const unsigned char* st = base + s * STAGE_BYTES;
+        const unsigned char* st = base + s * STAGE;
+        const unsigned char* xs = st + STAGE_BYTES;
 #pragma unroll
         for (int win = 0; win < 2; ++win) {
             const int ch = win * 4 + c;
@@ -144,8 +154,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16
             const uint4 a_hi = *reinterpret_cast<const uint4*>(st + r_hi * 128 + ((ch ^ (r_hi & 7)) << 4));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                uint4 b = make_uint4(0, 0, 0, 0);
-                if (xok[nt]) b = __ldg(reinterpret_cast<const uint4*>(xrow[nt] + (size_t)kc * KC + win * 32));
+                const int t = nt * 8 + g;                  // rows beyond M were filled with zeros by the copy
+                const uint4 b = *reinterpret_cast<const uint4*>(xs + t * 128 + ((ch ^ (t & 7)) << 4));
                 mma16816(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
                 mma16816(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
             }
@@ -190,8 +200,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __nv_bfloat16
                 for (int idx = ctid; idx < TR * TOK; idx += CONSUMERS * 32) {
                     const int t = idx / TR, r = idx % TR;
                     if (t < M && rt * TR + r < N) {
+                        const float* src = tile_ws + (size_t)r * TOK + t;
                         float sum = 0.f;
-                        for (int k = 0; k < contrib; ++k) sum += __ldcg(tile_ws + ((size_t)k * TR + r) * TOK + t);
+                        for (int k0 = 0; k0 < contrib; k0 += 8) {      // 8 independent loads in flight, added in share order
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                v[j] = k0 + j < contrib ? __ldcg(src + (size_t)(k0 + j) * TR * TOK) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) sum += v[j];
+                        }
                         out[(size_t)t * ldo + rt * TR + r] = cvt_out<OutT>(sum);
                     }
                 }
@@ -245,7 +263,18 @@ int get_weight_map(const void* W, int N, int K, CUtensorMap* out) {
 template <int NT, typename OutT>
 int launch(const CUtensorMap& map, const void* X, int ldx, void* out, int ldo, int M, int N, int K, float* workspace,
            int max_contrib, int* counters, int* error_word, int grid, cudaStream_t stream) {
-    const size_t smem = (size_t)NS * STAGE_BYTES + 2 * NS * 8 + 1024;
+    // the activations' map is made per call: their address changes from call to call
+    CUtensorMap xmap;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+        const cuuint32_t box[2] = {KC, NT * 8};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode_fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(X), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return -5;
+    }
+    const size_t smem = (size_t)NS * (STAGE_BYTES + NT * 8 * KC * 2) + 2 * NS * 8 + 1024;
     auto kern = gemm_stream_kernel<NT, OutT>;
     static bool configured = false;
     if (!configured) {
@@ -253,9 +282,8 @@ int launch(const CUtensorMap& map, const void* X, int ldx, void* out, int ldo, i
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<grid, THREADS, smem, stream>>>(map, (const __nv_bfloat16*)X, ldx, (OutT*)out, ldo, M, N, K, workspace,
-                                          max_contrib, counters, error_word);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(kern, dim3(grid), dim3(THREADS), smem, stream, map, xmap, (OutT*)out, ldo, M, N, K, workspace,
+                           max_contrib, counters, error_word);
 }
 
 }  // namespace

@@ -20,6 +20,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restr
                                           const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                           int H, int KV, int D, int page_size, float eps) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -89,7 +91,7 @@ MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w,
                                     cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (D % 4 || D / 2 > MAX_HALF) return -2;
-#define LAUNCH(T, WT) qk_norm_rope_cache_kernel<T, WT><<<dim3(T_, (H + 2 * KV + 3) / 4), 128, 0, stream>>>((T*)qkv, (const WT*)q_w, (const WT*)k_w, \
+#define LAUNCH(T, WT) return (int)launch_pdl(qk_norm_rope_cache_kernel<T, WT>, dim3(T_, (H + 2 * KV + 3) / 4), dim3(128), 0, stream, (T*)qkv, (const WT*)q_w, (const WT*)k_w, \
         inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, D, page_size, eps)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);

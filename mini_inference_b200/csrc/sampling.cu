@@ -28,6 +28,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
                               int* __restrict__ out) {
     __shared__ float best_v[NT / 32];
     __shared__ int best_i[NT / 32];
+    mi::pdl_trigger();
+    mi::pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temps ? temps[r] : 0.f;
@@ -59,6 +61,5 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
 MI_EXPORT int mi_sample(const float* logits, int ld, int rows, int vocab, const float* temps, const uint32_t* seeds,
                         const uint32_t* counters, int* out, cudaStream_t stream) {
     if (rows == 0) return 0;
-    sample_kernel<1024><<<rows, 1024, 0, stream>>>(logits, ld, vocab, temps, seeds, counters, out);
-    return (int)cudaGetLastError();
+    return (int)mi::launch_pdl(sample_kernel<1024>, dim3(rows), dim3(1024), 0, stream, logits, ld, vocab, temps, seeds, counters, out);
 }

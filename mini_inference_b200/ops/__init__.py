@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -60,6 +61,9 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
+        self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
+        self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
+        self._stream_plans, self._stream_counters, self._stream_error = {}, None, None
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
@@ -107,6 +111,11 @@ class CudaOps:
             self.launches += 1
             return out
         M, K = x.shape
+        if (self.stream_gemm and M <= 32 and w.shape[0] <= self.stream_max_cols and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            out = self._gemm_stream(x, w, out_dtype or x.dtype)
+            if out is not None:
+                return out
         if (self.skinny_gemm and M <= self.skinny_max_rows and w.shape[0] <= self.skinny_max_cols and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             N = w.shape[0]
@@ -124,6 +133,39 @@ class CudaOps:
             except TypeError:
                 return torch.mm(x, w.t()).to(out_dtype)
         return torch.mm(x, w.t())
+
+    def _gemm_stream(self, x, w, od):
+        """Persistent TMA weight-streaming product (csrc/gemm_stream.cu); None if the shape is not taken."""
+        M, K = x.shape
+        N = w.shape[0]
+        plan = self._stream_plans.get((M, N, K))
+        if plan is None:
+            g, rt, mc = _c.c_int(), _c.c_int(), _c.c_int()
+            rc = self.lib.mi_gemm_stream_plan(M, N, K, _c.byref(g), _c.byref(rt), _c.byref(mc))
+            plan = self._stream_plans[(M, N, K)] = None if rc else (g.value, rt.value, mc.value)
+        if not plan:
+            return None
+        _, row_tiles, max_contrib = plan
+        if self._stream_counters is None or self._stream_counters.numel() < row_tiles:
+            self._stream_counters = torch.zeros(max(row_tiles, 4096), dtype=torch.int32, device=x.device)
+            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
+        tok = 8 if M <= 8 else 16 if M <= 16 else 32
+        workspace = torch.empty(row_tiles * max_contrib * 128 * tok, dtype=torch.float32, device=x.device)
+        out = torch.empty((M, N), dtype=od, device=x.device)
+        rc = self.lib.mi_gemm_stream(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), _p(workspace),
+                                     _p(self._stream_counters), _p(self._stream_error), self._stream())
+        if rc == -2:
+            return None
+        _check(rc, "gemm_stream")
+        self.launches += 1
+        return out
+
+    def check_errors(self):
+        """Raises if a bounded wait inside a kernel ran out (synchronises the device)."""
+        if self._stream_error is not None and int(self._stream_error.item()) != 0:
+            code = int(self._stream_error.item())
+            self._stream_error.zero_()
+            raise RuntimeError(f"gemm_stream: a pipeline wait inside the kernel ran out (code {code})")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):

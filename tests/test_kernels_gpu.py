@@ -117,6 +117,27 @@ def test_gemm_skinny(ops, request, M, N, K):
         assert torch.equal(ops.linear(x[5:9], w, out_dtype=torch.float32), got[5:9])
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (6144, 2560), (100, 64), (517, 192), (19456, 2560), (2560, 9728), (128, 64)])
+def test_gemm_stream(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :K]      # strided rows
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    got = ops._gemm_stream(x, w, torch.float32)
+    assert got is not None
+    ops.check_errors()
+    want = x.double() @ w.double().T
+    assert ((got.double() - want).abs().max() / want.abs().max()).item() < 1e-5
+    got16 = ops._gemm_stream(x, w, torch.bfloat16)
+    close(got16, want, torch.bfloat16)
+    # same bits on a second call (the split's summation order is fixed) and alone vs in company
+    assert torch.equal(ops._gemm_stream(x, w, torch.float32), got)
+    assert torch.equal(ops._gemm_stream(x[:1], w, torch.float32), got[:1])
+    if M > 8:
+        assert torch.equal(ops._gemm_stream(x[5:9], w, torch.float32), got[5:9])
+    ops.check_errors()
+
+
 def make_meta(page_size, segs, num_pages, seed, tile=64):
     """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
     shaped like engine.batch.GroupMeta."""
