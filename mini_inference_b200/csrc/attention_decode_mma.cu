@@ -30,6 +30,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -38,13 +44,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 constexpr int DEC_WARPS = 4;
 
 template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 3)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
-                       float scale_log2, int window) {
+                       float scale_log2, int window, int* __restrict__ merge_counters) {
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
@@ -63,19 +69,22 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     const int b0 = blk_lo + s * per, b1 = min(b0 + per, blk_hi);
     const int* table_row = block_table + (size_t)seg * table_stride;
 
-    // query fragments, permuted: the 16 bytes at d = 32 j + 8 c of rows g and g + 8
-    uint32_t qa[KS][4];
-    {
+    // query fragments, permuted: the 16 bytes at d = 32 j + 8 c of rows g and g + 8.  They are the
+    // same for all warps and live in shared memory ([k-step][lane] x 16 bytes) to keep registers
+    // for the loads in flight.
+    uint4* q_frag = reinterpret_cast<uint4*>(smem + DEC_WARPS * 16 * (D + 2));
+    if (warp == 0) {
         const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
 #pragma unroll
         for (int j = 0; j < KS / 2; ++j) {
             uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
             if (g < G) r0 = *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + 32 * j + 8 * c);
             if (g + 8 < G) r1 = *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + 32 * j + 8 * c);
-            qa[2 * j][0] = r0.x; qa[2 * j][2] = r0.y; qa[2 * j + 1][0] = r0.z; qa[2 * j + 1][2] = r0.w;
-            qa[2 * j][1] = r1.x; qa[2 * j][3] = r1.y; qa[2 * j + 1][1] = r1.z; qa[2 * j + 1][3] = r1.w;
+            q_frag[(2 * j) * 32 + lane] = make_uint4(r0.x, r1.x, r0.y, r1.y);
+            q_frag[(2 * j + 1) * 32 + lane] = make_uint4(r0.z, r1.z, r0.w, r1.w);
         }
     }
+    __syncthreads();
 
     float o[NT][4];
 #pragma unroll
@@ -119,8 +128,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
             sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
             for (int j = 0; j < KS / 2; ++j) {
-                mma_bf16_16816(sc[nt], qa[2 * j], kreg[nt][j].x, kreg[nt][j].y);
-                mma_bf16_16816(sc[nt], qa[2 * j + 1], kreg[nt][j].z, kreg[nt][j].w);
+                const uint4 qa0 = q_frag[(2 * j) * 32 + lane], qa1 = q_frag[(2 * j + 1) * 32 + lane];
+                mma_bf16_16816(sc[nt], qa0, kreg[nt][j].x, kreg[nt][j].y);
+                mma_bf16_16816(sc[nt], qa1, kreg[nt][j].z, kreg[nt][j].w);
             }
         }
         if (blk + DEC_WARPS < b1) load_k(blk + DEC_WARPS);          // next block's keys fly during the rest
@@ -215,23 +225,82 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
             if (d == 0) lse_part[pi] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
         }
     }
+    if (S == 1 || merge_counters == nullptr) return;
+
+    // The block that finishes last among the S splits of this (request, kv head) merges them:
+    // out = sum_s e^(lse_s - max) o_s / sum_s e^(lse_s - max), splits added in index order.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(&merge_counters[blockIdx.x * KV + kvh], 1) == S - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+        const int row = idx / D, d = idx % D, h = kvh * G + row;
+        const size_t base = ((size_t)blockIdx.x * H + h) * S;
+        float mx = -INFINITY, num = 0.f, den = 0.f;
+        for (int k0 = 0; k0 < S; k0 += 8) {                 // 8 independent loads in flight
+            float l[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) l[j] = k0 + j < S ? __ldcg(lse_part + base + k0 + j) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx = fmaxf(mx, l[j]);
+        }
+        for (int k0 = 0; k0 < S; k0 += 8) {
+            float l[8], v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool ok = k0 + j < S;
+                l[j] = ok ? __ldcg(lse_part + base + k0 + j) : -INFINITY;
+                v[j] = ok ? __ldcg(o_part + (base + k0 + j) * D + d) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = expf(l[j] - mx);
+                den += w;
+                num += w * v[j];
+            }
+        }
+        out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(num / den);
+    }
+    if (threadIdx.x == 0) merge_counters[blockIdx.x * KV + kvh] = 0;       // ready for the next call
 }
+
+MI_EXPORT int mi_attn_decode_mma_fused(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                       float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                       int window, int* merge_counters, cudaStream_t stream);
 
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                  const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                  int table_stride, int H, int KV, int D, int ps, int splits, float scale, int window,
                                  cudaStream_t stream) {
+    return mi_attn_decode_mma_fused(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode,
+                                    seg_q_start, seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale,
+                                    window, nullptr, stream);
+}
+
+// merge_counters: int32 [num_decode * KV], zero before the first call (the kernel leaves them zero).
+// With it the splits are merged by the last block to finish and no separate merge launch is needed;
+// null keeps the partial outputs for mi_attn_decode_merge.
+MI_EXPORT int mi_attn_decode_mma_fused(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                       float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                       int window, int* merge_counters, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
-    const size_t smem = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t smem = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float) + (size_t)(D / 16) * 32 * 16;
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD) do { \
         return (int)launch_pdl(attn_decode_mma_kernel<DD>, grid, dim3(DEC_WARPS * 32), smem, stream, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
-            H, KV, ps, scale_log2, window); } while (0)
+            H, KV, ps, scale_log2, window, merge_counters); } while (0)
     if (D == 128) LAUNCH(128); else LAUNCH(64);
 #undef LAUNCH
     return (int)cudaGetLastError();

@@ -64,6 +64,10 @@ class LLM:
         self.sampler = Sampler(self.ops, args.seed)
         self.eos_ids = set(self.model.spec.eos_token_ids)
         self.graphs = None
+        self.linear_tuning = None
+        if args.cuda_graphs and self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_linear"):
+            self.linear_tuning = self.ops.tune_linear(self.model.matrix_weights(),
+                                                      {tuple(self.model.lm_head.shape): torch.float32})
         if args.cuda_graphs:
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self.runner, args.max_num_seqs)

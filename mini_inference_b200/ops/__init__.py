@@ -63,6 +63,10 @@ class CudaOps:
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
+        self._sample_slots = self._sample_arrivals = None
+        self.fused_merge = True              # the last split block to finish merges the splits (no merge launch)
+        self._merge_counters = None
+        self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
         self._stream_plans, self._stream_counters, self._stream_error = {}, None, None
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
@@ -111,12 +115,16 @@ class CudaOps:
             self.launches += 1
             return out
         M, K = x.shape
-        if (self.stream_gemm and M <= 32 and w.shape[0] <= self.stream_max_cols and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+        choice = self._linear_choice.get((self._row_bucket(M), w.shape[0], K)) if self._linear_choice else None
+        if choice == "library":
+            return self._library_linear(x, w, out_dtype)
+        if (self.stream_gemm and choice in (None, "stream") and M <= 32 and w.shape[0] <= self.stream_max_cols and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             out = self._gemm_stream(x, w, out_dtype or x.dtype)
             if out is not None:
                 return out
-        if (self.skinny_gemm and M <= self.skinny_max_rows and w.shape[0] <= self.skinny_max_cols and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+        if (self.skinny_gemm and (choice == "skinny" or (choice is None and M <= self.skinny_max_rows
+                                                         and w.shape[0] <= self.skinny_max_cols)) and M <= 64 and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             N = w.shape[0]
             od = out_dtype or x.dtype
@@ -127,12 +135,84 @@ class CudaOps:
                 return out
             if err != -2:
                 _check(err, "gemm_skinny")
+        return self._library_linear(x, w, out_dtype)
+
+    @staticmethod
+    def _library_linear(x, w, out_dtype):
         if out_dtype is not None and out_dtype != x.dtype:
             try:
                 return torch.mm(x, w.t(), out_dtype=out_dtype)
             except TypeError:
                 return torch.mm(x, w.t()).to(out_dtype)
         return torch.mm(x, w.t())
+
+    ROW_BUCKETS = (1, 2, 4, 8, 16, 32)
+
+    def _row_bucket(self, M):
+        for b in self.ROW_BUCKETS:
+            if M <= b:
+                return b
+        return 0
+
+    def tune_linear(self, weights, out_dtypes=None, iters=12):
+        """Per weight shape and row-count bucket, time this package's few-row kernels against the
+        library GEMM on the model's own weights and remember the fastest.  The reference does the
+        same kind of start-up timing to choose a weight layout per shape
+        (engine/core/fused_linear.py:51-94); rotating over the layers' real weights keeps the L2
+        from flattering anyone.  weights: bfloat16 [N, K] tensors; out_dtypes: {(N, K): dtype}."""
+        groups = {}
+        for w in weights:
+            if w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous():
+                groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+        saved = (self.stream_gemm, self.skinny_gemm, self.skinny_max_rows, self.skinny_max_cols, self.stream_max_cols)
+        table, report = {}, {}
+        try:
+            self._linear_choice = None
+            for (N, K), ws in groups.items():
+                od = (out_dtypes or {}).get((N, K))
+                # one weight cannot defeat the L2 by rotation; leave such shapes to the default rule
+                if len(ws) * N * K * 2 < (256 << 20) and N * K * 2 < (256 << 20):
+                    continue
+                for M in self.ROW_BUCKETS:
+                    x = torch.randn(M, K, device=ws[0].device, dtype=torch.bfloat16)
+                    times = {}
+                    for name in ("library", "stream", "skinny"):
+                        if name == "stream" and K % 64:
+                            continue
+                        if name == "skinny" and K % 32:
+                            continue
+                        self.stream_gemm, self.skinny_gemm = name == "stream", name == "skinny"
+                        self.skinny_max_rows, self.skinny_max_cols, self.stream_max_cols = 64, 1 << 30, 1 << 30
+                        times[name] = self._time_in_graph(lambda i: self.linear(x, ws[i % len(ws)], out_dtype=od), iters)
+                    best = min(times, key=times.get)
+                    table[(M, N, K)] = best
+                    report[f"{N}x{K} M<={M}"] = {k: round(v, 2) for k, v in times.items()} | {"best": best}
+        finally:
+            self.stream_gemm, self.skinny_gemm, self.skinny_max_rows, self.skinny_max_cols, self.stream_max_cols = saved
+        self._linear_choice = table
+        self.check_errors()
+        return report
+
+    def _time_in_graph(self, fn, iters):
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            fn(0)
+            fn(1)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(i)
+        graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(self.device)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize(self.device)
+        return start.elapsed_time(stop) * 1e3 / iters
 
     def _gemm_stream(self, x, w, od):
         """Persistent TMA weight-streaming product (csrc/gemm_stream.cu); None if the shape is not taken."""
@@ -180,13 +260,25 @@ class CudaOps:
         return qkv[:, :H * D]
 
     # ---------------------------------------------------------------- attention over the pages
-    def choose_splits(self, ctas, max_kv_len):
+    def choose_splits(self, ctas, max_kv_len, per_sm=2):
         """Enough blocks to fill the GPU about twice, never more splits than the longest
         request has 256-key pieces (kernels/paged_attention/decode_triton.py:114-120)."""
         if self.force_splits:
             return self.force_splits
-        slots = 2 * self.NUM_SMS                           # two blocks are resident per SM: stay within one wave
-        return max(1, min(slots // ctas, math.ceil(max_kv_len / 256), 32))
+        slots = per_sm * self.NUM_SMS                      # blocks resident at once
+        most = max(1, min(math.ceil(max_kv_len / 256), 32))
+        if ctas * most <= slots:
+            return most
+        # more blocks than fit at once: take the fewest splits whose last wave is at least 85 % full
+        best, best_eff = 1, 0.0
+        for S in range(1, most + 1):
+            total = ctas * S
+            eff = total / (math.ceil(total / slots) * slots)
+            if eff >= 0.85:
+                return S
+            if eff > best_eff:
+                best, best_eff = S, eff
+        return best
 
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
         T = q.shape[0]
@@ -209,20 +301,28 @@ class CudaOps:
             self.launches += 1
         fast_decode = fast and H // KV <= 16 and meta.page_size % 16 == 0
         if meta.num_decode:
-            S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len)
+            S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len,
+                                   3 if fast_decode else 2)
             o_part = lse = None
             if S > 1:
                 o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)
                 lse = torch.empty((meta.num_decode, H, S), dtype=torch.float32, device=q.device)
         if meta.num_decode and fast_decode:
-            _check(self.lib.mi_attn_decode_mma(
+            counters = None
+            if S > 1 and self.fused_merge:
+                need = meta.num_decode * KV
+                if self._merge_counters is None or self._merge_counters.numel() < need:
+                    self._merge_counters = torch.zeros(max(need, 8192), dtype=torch.int32, device=q.device)
+                counters = self._merge_counters
+            _check(self.lib.mi_attn_decode_mma_fused(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
-                H, KV, D, meta.page_size, S, _c.c_float(scale), win, self._stream()), "attn_decode_mma")
-            if S > 1:
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), self._stream()), "attn_decode_mma")
+            self.launches += 1
+            if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,
                                                      _p(meta.seg_q_start), H, D, S, code, self._stream()), "attn_merge")
-            self.launches += 2 if S > 1 else 1
+                self.launches += 1
         elif meta.num_decode:
             _check(self.lib.mi_attn_decode_generic(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
@@ -241,6 +341,15 @@ class CudaOps:
         assert logits.dtype == torch.float32 and logits.stride(1) == 1
         R, V = logits.shape
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        if V >= 16384 and R <= 4096:                     # several blocks per row
+            if self._sample_slots is None:
+                self._sample_slots = torch.zeros(4096, dtype=torch.int64, device=logits.device)
+                self._sample_arrivals = torch.zeros(4096, dtype=torch.int32, device=logits.device)
+            _check(self.lib.mi_sample_split(_p(logits), logits.stride(0), R, V, _p(temperatures), _p(seeds), _p(counters),
+                                            _p(out), _p(self._sample_slots), _p(self._sample_arrivals), self._stream()),
+                   "sample")
+            self.launches += 1
+            return out
         _check(self.lib.mi_sample(_p(logits), logits.stride(0), R, V, _p(temperatures), _p(seeds), _p(counters),
                                   _p(out), self._stream()), "sample")
         self.launches += 1

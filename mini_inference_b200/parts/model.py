@@ -69,6 +69,15 @@ class DecoderModel:
         self.embedding = tensors[self.spec.embedding_name]
         self.lm_head = self.embedding if self.spec.lm_head_name is None else tensors[self.spec.lm_head_name]
 
+    def matrix_weights(self):
+        """The matrices the model multiplies by (after the parts fused what they fuse)."""
+        out = []
+        for block in self.blocks:
+            for part in (block.mixer, block.feed_forward):
+                out += [v for v in vars(part).values() if isinstance(v, torch.Tensor) and v.dim() == 2]
+        out.append(self.lm_head)
+        return out
+
     # ---------------------------------------------------------------- cache needs
     def cache_needs(self):
         """Per execution step: the mixer's need, or None when the step reads another's cache."""

@@ -101,8 +101,9 @@ def test_gemm_skinny(ops, request, M, N, K):
     g = torch.Generator().manual_seed(M * 1000 + N)
     x = torch.randn(M, K + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :K]      # strided rows
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    ops.skinny_max_rows, ops.skinny_max_cols = 64, 1 << 30     # this test is about the package's own kernel
-    request.addfinalizer(lambda: (setattr(ops, "skinny_max_rows", 16), setattr(ops, "skinny_max_cols", 4096)))
+    ops.skinny_max_rows, ops.skinny_max_cols, ops.stream_gemm = 64, 1 << 30, False     # this test is about the skinny kernel
+    request.addfinalizer(lambda: (setattr(ops, "skinny_max_rows", 16), setattr(ops, "skinny_max_cols", 4096),
+                                  setattr(ops, "stream_gemm", True)))
     before = ops.launches
     got = ops.linear(x, w, out_dtype=torch.float32)
     assert ops.launches == before + 1                     # the package's own kernel ran
@@ -208,14 +209,16 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
     # make one far key of the long decode stand out, so that a lost or misplaced key shows
     kc[meta.block_table[5, 2].long(), :, 3, :] *= 4.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-    for fast in (True, False):
+    for fast, fused in ((True, True), (True, False), (False, False)):
         for splits in (None, 1, 3):
-            ops.force_splits, ops.fast_attention = splits, fast
+            ops.force_splits, ops.fast_attention, ops.fused_merge = splits, fast, fused
             try:
                 got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+                got2 = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)    # counters were left clean
             finally:
-                ops.force_splits, ops.fast_attention = None, True
+                ops.force_splits, ops.fast_attention, ops.fused_merge = None, True, True
             close(got, want, dtype)
+            assert torch.equal(got, got2)
 
 
 def test_sampling(ops):
@@ -234,6 +237,24 @@ def test_sampling(ops):
     # the chosen token's perturbed score is the row's maximum (up to the rounding of log)
     assert ((top - scores[torch.arange(6), got]).abs() < 1e-4 * top.abs().clamp_min(1)).all()
     assert got[0] == logits[0].argmax().item() and got[4] == logits[4].argmax().item()
+
+
+def test_sampling_large_vocabulary(ops):
+    """The several-blocks-per-row path: same tokens as the reference, ties to the lowest index, twice in a row."""
+    g = torch.Generator().manual_seed(8)
+    V = 151936
+    logits = (torch.randn(5, V, generator=g) * 2).to(DEV)
+    logits[1, 70000] = logits[1, 150000] = logits[1, 9] = logits[1].max() + 1
+    temps = torch.tensor([0.0, 0.0, 0.9, 1.3, 0.0], device=DEV)
+    seeds = torch.tensor([3, 4, 5, 6, 7], dtype=torch.int32, device=DEV)
+    counters = torch.tensor([0, 9, 2, 30, 4], dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        got = ops.sample(logits, temps, seeds, counters).cpu().long()
+        assert got[1] == 9 and got[0] == logits[0].argmax().item() and got[4] == logits[4].argmax().item()
+        scores = perturbed_scores(logits.cpu(), temps.cpu(), seeds.cpu(), counters.cpu())
+        top = scores.max(-1).values
+        assert ((top - scores[torch.arange(5), got]).abs() < 1e-4 * top.abs().clamp_min(1)).all()
+        assert torch.equal(ops.argmax(logits).cpu().long(), logits.argmax(-1).cpu())
 
 
 def test_sampling_distribution(ops):
