@@ -61,6 +61,8 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
+        self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"      # many-row products on the tcgen05 kernel
+        self.tc_min_rows = 128
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
         self._sample_slots = self._sample_arrivals = None
@@ -115,6 +117,11 @@ class CudaOps:
             self.launches += 1
             return out
         M, K = x.shape
+        if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            out = self._gemm_tc(x, w, out_dtype or x.dtype)
+            if out is not None:
+                return out
         choice = self._linear_choice.get((self._row_bucket(M), w.shape[0], K)) if self._linear_choice else None
         if choice == "library":
             return self._library_linear(x, w, out_dtype)
@@ -240,12 +247,28 @@ class CudaOps:
         self.launches += 1
         return out
 
+    def _gemm_tc(self, x, w, od):
+        """tcgen05 + TMA product for many rows (csrc/gemm_tc.cu); None if the shape is not taken."""
+        M, K = x.shape
+        N = w.shape[0]
+        if self._stream_error is None:
+            self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
+            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
+        out = torch.empty((M, N), dtype=od, device=x.device)
+        rc = self.lib.mi_gemm_tc(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), _p(self._stream_error),
+                                 self._stream())
+        if rc == -2:
+            return None
+        _check(rc, "gemm_tc")
+        self.launches += 1
+        return out
+
     def check_errors(self):
         """Raises if a bounded wait inside a kernel ran out (synchronises the device)."""
         if self._stream_error is not None and int(self._stream_error.item()) != 0:
             code = int(self._stream_error.item())
             self._stream_error.zero_()
-            raise RuntimeError(f"gemm_stream: a pipeline wait inside the kernel ran out (code {code})")
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):

@@ -139,6 +139,21 @@ def test_gemm_stream(ops, M, N, K):
     ops.check_errors()
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (200, 517, 192), (2048, 2560, 4096), (300, 6144, 2560),
+                                   (1, 256, 64), (129, 300, 640)])
+def test_gemm_tc(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :K]
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    got = ops._gemm_tc(x, w, torch.float32)
+    assert got is not None
+    ops.check_errors()
+    want = x.double() @ w.double().T
+    assert ((got.double() - want).abs().max() / want.abs().max()).item() < 1e-5
+    close(ops._gemm_tc(x, w, torch.bfloat16), want, torch.bfloat16)
+    ops.check_errors()
+
+
 def make_meta(page_size, segs, num_pages, seed, tile=64):
     """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
     shaped like engine.batch.GroupMeta."""
