@@ -97,7 +97,7 @@ def bench_attention(args, ops, peak):
             page_size=ps, tile=64, block_table=table, max_pages=pages_per_seq, seg_q_start=ar,
             seg_pos0=torch.full((B,), args.ctx - 1, dtype=torch.int32, device="cuda"),
             seg_kv_len=torch.full((B,), args.ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B],
-            prefill_tiles=None, num_decode=B, num_prefill_tiles=0, max_kv_len=args.ctx, num_tokens=B)
+            prefill_tiles=None, prefill_tiles2=None, num_prefill_tiles2=0, num_decode=B, num_prefill_tiles=0, max_kv_len=args.ctx, num_tokens=B)
         q = torch.randn(B, H * D, device="cuda", dtype=torch.bfloat16)
         for label, flag in (("tensor-core", True), ("generic", False)):
             ops.fast_attention = flag

@@ -1,0 +1,283 @@
+// Paged attention for prompt portions on the 5th-generation tensor cores (tcgen05 + tensor
+// memory + TMA), bfloat16, head size 64 or 128, page size a multiple of 8.
+//
+// Reference (davidjoyme/mini-inference engine/core/model_runner.py:161-173): gather the context,
+// call the library attention once per request.  The mma.sync kernel in attention_prefill_mma.cu
+// already reads the pages in place, but the legacy tensor path of this GPU saturates near
+// 160 TFLOP/s; this kernel moves both products onto tcgen05:
+//   block = 128 query rows of one entry x one query head, 6 warps
+//   warp 0   TMA: the query tile once, then 64-key K and V tiles page by page through the block
+//            table into a two-stage ring (128-byte swizzle, the layout the MMA descriptors expect)
+//   warp 1   one thread issues S = Q K^T (tcgen05.mma, both operands in shared memory, S in 64
+//            columns of tensor memory) and O += P V (P read from tensor memory, V from shared
+//            memory as an MN-major operand, O in D columns of tensor memory)
+//   warps 2-5  one query row per thread (= one tensor-memory lane): read S, mask by position,
+//            online softmax in float32 (base 2), write P as packed bfloat16 back to tensor
+//            memory; the running output is only rescaled when the row maximum grew by more than
+//            2^8 (the exponent offset is kept otherwise), which makes the correction rare;
+//            at the end divide by the row sum and store.
+// Two blocks fit on an SM (256 tensor-memory columns and 96 KB of shared memory each), so one
+// block's softmax overlaps the other's MMAs.  Every mbarrier wait is bounded.
+#include "sm100.cuh"
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <math.h>
+
+using namespace mi;
+using namespace mi::sm100;
+
+namespace {
+
+constexpr int BQ = 128, BKV = 64;
+constexpr int ATT_THREADS = 192;
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
+                       const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_stride,
+                       int H, int KV, int ps, float scale_log2, int window, int* __restrict__ error_word) {
+    constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a head
+    constexpr int Q_BYTES = BQ * D * 2, KV_BYTES = BKV * D * 2;
+    constexpr int TMEM_COLS = 256;                       // S: 64, P: 32, O: D (<= 128)
+    constexpr uint32_t S_COL = 0, P_COL = 64, O_COL = 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // [Q][K0][K1][V0][V1][barriers]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + Q_BYTES + 4 * KV_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    const uint32_t sQ = smem_u32(base), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES;
+    const uint32_t q_full = smem_u32(bars), kv_full = smem_u32(bars + 1), kv_empty = smem_u32(bars + 3),
+                   s_full = smem_u32(bars + 5), p_ready = smem_u32(bars + 6), o_done = smem_u32(bars + 7);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int tile = gridDim.x - 1 - blockIdx.x;         // later tiles see more keys: start them first
+    const int seg = tiles[2 * tile], r0 = tiles[2 * tile + 1];
+    const int h = blockIdx.y, kvh = h / (H / KV);
+    const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
+    const int rows = min(BQ, n - r0);
+    const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
+    const int kt_lo = window > 0 ? max(0, p_first - window + 1) / BKV : 0;
+    const int kt_hi = p_last / BKV;
+    const int nt = kt_hi - kt_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(kv_full, 1); mbar_init(kv_full + 8, 1);
+        mbar_init(kv_empty, 1); mbar_init(kv_empty + 8, 1);
+        mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+        mbar_init_fence();
+        tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_trigger();
+    pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- loads
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int hb = 0; hb < HALVES; ++hb)
+                tma_load_2d(sQ + hb * (BQ * 128), &qmap, h * D + hb * 64, qs + r0, q_full);
+            const int* table_row = block_table + (size_t)seg * table_stride;
+            const int pages_per_tile = BKV / ps;
+            for (int i = 0; i < nt; ++i) {
+                const int s = i & 1, kt = kt_lo + i;
+                if (i >= 2 && !mbar_wait(kv_empty + 8 * s, ((i >> 1) - 1) & 1)) { atomicExch(error_word, 21); break; }
+                mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
+                for (int pg = 0; pg < pages_per_tile; ++pg) {
+                    const int j = kt * BKV + pg * ps;
+                    const int page = j <= p_last ? table_row[j / ps] : 0;          // beyond the last row's keys: null page
+                    const int y = (page * KV + kvh) * ps;
+#pragma unroll
+                    for (int hb = 0; hb < HALVES; ++hb) {
+                        const uint32_t off = s * KV_BYTES + hb * (BKV * 128) + pg * ps * 128;
+                        tma_load_2d(sK + off, &kmap, hb * 64, y, kv_full + 8 * s);
+                        tma_load_2d(sV + off, &vmap, hb * 64, y, kv_full + 8 * s);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, false);     // S[128 x 64]  = Q (K-major) * K^T (K-major)
+            const uint32_t idesc_o = umma_idesc_bf16(BQ, D, true);        // O[128 x D]  += P (tensor memory) * V (MN-major)
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicExch(error_word, 22);
+            auto issue_qk = [&](int i) {
+                const int s = i & 1;
+                if (!mbar_wait(kv_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 23); ok = false; return; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t a = sQ + (ks / 4) * (BQ * 128) + (ks % 4) * 32;
+                    const uint32_t b = sK + s * KV_BYTES + (ks / 4) * (BKV * 128) + (ks % 4) * 32;
+                    umma_ss(tmem + S_COL, umma_desc_sw128(a, 16, 1024), umma_desc_sw128(b, 16, 1024), idesc_s, ks != 0);
+                }
+                umma_commit(s_full);
+            };
+            if (ok) issue_qk(0);
+            for (int i = 0; i < nt && ok; ++i) {
+                const int s = i & 1;
+                if (!mbar_wait(p_ready, i & 1)) { atomicExch(error_word, 24); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+                    const uint32_t b = sV + s * KV_BYTES + kk * (16 * 128);
+                    umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, umma_desc_sw128(b, BKV * 128, 1024), idesc_o, (i | kk) != 0);
+                }
+                umma_commit(kv_empty + 8 * s);                 // K and V of this stage are free once these finish
+                if (i + 1 < nt) issue_qk(i + 1);
+                else umma_commit(o_done);
+            }
+        }
+    } else {
+        // ---------------- softmax: thread <-> query row <-> tensor-memory lane
+        const int lg = warp & 3;
+        const int row = lg * 32 + lane;                        // row of the tile
+        const int p_row = pos0 + r0 + row;
+        const uint32_t lane_addr = tmem + ((uint32_t)(lg * 32) << 16);
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < nt && ok; ++i) {
+            const int kt = kt_lo + i;
+            if (!mbar_wait(s_full, i & 1)) { atomicExch(error_word, 25); ok = false; break; }
+            tc_fence_after();
+            uint32_t r[64];                                     // the row's 64 scores, scaled and masked in place
+            tmem_ld32(lane_addr + S_COL, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld32(lane_addr + S_COL + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tmem_wait_ld();
+            float mx = -INFINITY;
+            const bool inside = kt * BKV + BKV - 1 <= p_row && (window <= 0 || kt * BKV > p_row - window);
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                const float v = __uint_as_float(r[c]) * scale_log2;
+                const int j = kt * BKV + c;
+                const bool vis = inside || (j <= p_row && (window <= 0 || j > p_row - window));
+                const float sv = vis ? v : -INFINITY;
+                r[c] = __float_as_uint(sv);
+                mx = fmaxf(mx, sv);
+            }
+            // keep the exponent offset unless the maximum grew by more than 2^8: rescaling O is then rare
+            float alpha = 1.f;
+            bool rescale = false;
+            if (mx > m_ref + 8.f) {
+                alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                rescale = i > 0 && m_ref != -INFINITY;
+                m_ref = mx;
+                l *= alpha;
+            }
+            const float off = m_ref == -INFINITY ? 0.f : m_ref;
+            uint32_t pk[32];
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = exp2f(__uint_as_float(r[2 * c]) - off), p1 = exp2f(__uint_as_float(r[2 * c + 1]) - off);
+                sum += p0 + p1;
+                __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                pk[c] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            l += sum;
+            tmem_st32(lane_addr + P_COL, pk);
+            if (__any_sync(0xffffffffu, rescale)) {            // the previous O += P V is complete (s_full implies it)
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(lane_addr + O_COL + c * 32, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                    tmem_st32(lane_addr + O_COL + c * 32, o);
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(p_ready);
+        }
+        // ---------------- epilogue
+        if (ok && !mbar_wait(o_done, 0)) { atomicExch(error_word, 26); ok = false; }
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* orow = out + ((size_t)(qs + r0 + row) * H + h) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(lane_addr + O_COL + c * 32, o);
+                tmem_wait_ld();
+                if (row < rows) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 w;
+                        uint32_t* ww = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[8 * v4 + 2 * e]) * inv,
+                                                                      __uint_as_float(o[8 * v4 + 2 * e + 1]) * inv);
+                            ww[e] = *reinterpret_cast<uint32_t*>(&hh);
+                        }
+                        reinterpret_cast<uint4*>(orow + c * 32)[v4] = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+std::mutex att_mutex;
+std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> cache_maps;
+
+bool cache_map(const void* cache, long long rows, int D, int ps, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(att_mutex);
+    auto key = std::make_tuple(cache, (int)(rows & 0x7fffffff), (int)(rows >> 31), D, ps);
+    auto it = cache_maps.find(key);
+    if (it == cache_maps.end()) {
+        CUtensorMap m;
+        if (!sm100_host::make_map_bf16(&m, cache, (uint64_t)rows, D, D, ps, 64)) return false;
+        it = cache_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+
+}  // namespace
+
+// tiles: (entry, first row) of 128-row tiles.  cache_rows = pages (with the null page) * KV * page_size.
+MI_EXPORT int mi_attn_prefill_tc(const void* q, int q_stride, int num_tokens, const void* k_cache, const void* v_cache,
+                                 long long cache_rows, void* out, const int* tiles, int num_tiles, const int* seg_q_start,
+                                 const int* seg_pos0, const int* block_table, int table_stride, int H, int KV, int D,
+                                 int ps, int tile_rows, float scale, int window, int* error_word, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8 || ps % 8 || BKV % ps || ((uintptr_t)q % 16)) return -2;
+    CUtensorMap qmap, kmap, vmap;
+    if (!sm100_host::make_map_bf16(&qmap, q, num_tokens, (uint64_t)H * D, q_stride, BQ, 64)) return -5;
+    if (!cache_map(k_cache, cache_rows, D, ps, &kmap) || !cache_map(v_cache, cache_rows, D, ps, &vmap)) return -5;
+    const size_t smem = (size_t)BQ * D * 2 + 4 * (size_t)BKV * D * 2 + 8 * 8 + 16 + 1024;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(num_tiles, H);
+#define LAUNCH(DD, IDX) do { \
+        static bool configured = false; \
+        if (!configured) { \
+            cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+            configured = true; \
+        } \
+        return (int)launch_pdl(attn_prefill_tc_kernel<DD>, grid, dim3(ATT_THREADS), smem, stream, qmap, kmap, vmap, \
+                               (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_stride, H, KV, ps, \
+                               scale_log2, window, error_word); \
+    } while (0)
+    if (D == 128) LAUNCH(128, 0);
+    LAUNCH(64, 1);
+#undef LAUNCH
+}

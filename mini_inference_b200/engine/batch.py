@@ -11,7 +11,7 @@ arrays in ONE host buffer that reaches the device in one copy:
                seg_kv_len (keys it sees at its last token), seg_slot (state slot),
                per cache group: block_table [S, pages] by page index (0 = no page)
   work lists   decode_segs (entries that feed one token), prefill_tiles (entry, first row)
-               for every tile of `tile` rows of the longer entries
+               for every tile of `tile` rows of the longer entries (prefill_tiles2: 2 * tile rows)
   logit_rows   flat rows whose logits are wanted
 
 Only wanted rows reach the final norm and the head; the reference computes a row per chunk
@@ -69,6 +69,7 @@ class StepBatch:
         token_seg = np.repeat(np.arange(S, dtype=np.int32), lens)
         decode = [i for i, n in enumerate(lens) if n == 1]
         tiles = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, tile)]
+        tiles2 = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, 2 * tile)]
         rows = [int(q_start[i]) + w for i, e in enumerate(entries) for w in e.want]
         self.num_decode, self.num_prefill_tiles, self.num_logit_rows = len(decode), len(tiles), len(rows)
         self.host = {"seg_q_start": q_start, "seg_pos0": np.asarray(pos0, dtype=np.int32),
@@ -82,6 +83,7 @@ class StepBatch:
             "seg_slot": np.asarray([e.seq.slot for e in entries], dtype=np.int32),
             "decode_segs": np.asarray(decode, dtype=np.int32),
             "prefill_tiles": np.asarray(tiles, dtype=np.int32).reshape(-1),
+            "prefill_tiles2": np.asarray(tiles2, dtype=np.int32).reshape(-1),
             "logit_rows": np.asarray(rows, dtype=np.int32),
         }
         seqs = [e.seq for e in entries]
@@ -112,6 +114,8 @@ class StepBatch:
                   "seg_slot", "decode_segs", "logit_rows"):
             setattr(self, k, view(k))
         self.prefill_tiles = view("prefill_tiles").view(-1, 2)
+        self.prefill_tiles2 = view("prefill_tiles2").view(-1, 2)          # the same rows in tiles twice as tall
+        self.num_prefill_tiles2 = len(tiles2)
         self.groups = [GroupMeta(self, cache.page_size, view(f"slots{gi}"),
                                  view(f"table{gi}").view(S, max_pages), max_pages)
                        for gi in range(len(cache.kv_groups))]

@@ -63,6 +63,7 @@ class CudaOps:
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
         self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"      # many-row products on the tcgen05 kernel
         self.tc_min_rows = 128
+        self.tc_attention = os.environ.get("MI_TC_ATTENTION", "1") == "1"    # prompt attention on the tcgen05 kernel
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
         self._sample_slots = self._sample_arrivals = None
@@ -310,7 +311,20 @@ class CudaOps:
         code, win = _code(q.dtype), int(window or 0)
         fast = (self.fast_attention and q.dtype == torch.bfloat16 and D in (64, 128) and q.stride(0) % 8 == 0
                 and q.data_ptr() % 16 == 0)
-        if meta.num_prefill_tiles and fast and meta.tile == 64:
+        tc = (fast and self.tc_attention and meta.num_prefill_tiles and meta.tile == 64 and meta.page_size % 8 == 0
+              and 64 % meta.page_size == 0 and getattr(meta, "num_prefill_tiles2", 0))
+        if tc:
+            if self._stream_error is None:
+                self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
+                self._stream_error = torch.zeros(1, dtype=torch.int32, device=q.device)
+            rc = self.lib.mi_attn_prefill_tc(
+                _p(q), q.stride(0), T, _p(k_cache), _p(v_cache), _c.c_longlong(k_cache.shape[0] * KV * meta.page_size),
+                _p(out), _p(meta.prefill_tiles2), meta.num_prefill_tiles2, _p(meta.seg_q_start), _p(meta.seg_pos0),
+                _p(meta.block_table), meta.max_pages, H, KV, D, meta.page_size, 128, _c.c_float(scale), win,
+                _p(self._stream_error), self._stream())
+            _check(rc, "attn_prefill_tc")
+            self.launches += 1
+        elif meta.num_prefill_tiles and fast and meta.tile == 64:
             _check(self.lib.mi_attn_prefill_mma(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
                 _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,

@@ -173,11 +173,13 @@ def make_meta(page_size, segs, num_pages, seed, tile=64):
                             for s, (p, n) in enumerate(segs)]).astype(np.int32)
     decode = [s for s, (_, n) in enumerate(segs) if n == 1]
     tiles = [(s, r) for s, (_, n) in enumerate(segs) if n > 1 for r in range(0, n, tile)]
+    tiles2 = [(s, r) for s, (_, n) in enumerate(segs) if n > 1 for r in range(0, n, 2 * tile)]
     t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
     return types.SimpleNamespace(
         page_size=page_size, tile=tile, positions=t(positions), slots=t(slots), block_table=t(table),
         max_pages=max_pages, seg_q_start=t(q_start), seg_pos0=t([p for p, _ in segs]), seg_kv_len=t(kv_len),
-        decode_segs=t(decode), prefill_tiles=t(tiles).view(-1, 2), num_decode=len(decode),
+        decode_segs=t(decode), prefill_tiles=t(tiles).view(-1, 2), prefill_tiles2=t(tiles2).view(-1, 2),
+        num_prefill_tiles2=len(tiles2), num_decode=len(decode),
         num_prefill_tiles=len(tiles), max_kv_len=max(kv_len), num_tokens=int(q_start[-1]))
 
 
@@ -227,13 +229,37 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
     for fast, fused in ((True, True), (True, False), (False, False)):
         for splits in (None, 1, 3):
             ops.force_splits, ops.fast_attention, ops.fused_merge = splits, fast, fused
+            ops.tc_attention = splits != 3               # prompt portions: tcgen05 kernel, and the mma.sync kernel
             try:
                 got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
                 got2 = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)    # counters were left clean
             finally:
-                ops.force_splits, ops.fast_attention, ops.fused_merge = None, True, True
+                ops.force_splits, ops.fast_attention, ops.fused_merge, ops.tc_attention = None, True, True, True
             close(got, want, dtype)
             assert torch.equal(got, got2)
+            ops.check_errors()
+
+
+@pytest.mark.parametrize("H,KV,D,page", [(8, 2, 128, 16), (4, 4, 64, 8), (6, 1, 128, 32), (2, 2, 64, 64)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prefill_attention_long(ops, H, KV, D, page, window):
+    """Portions of hundreds of rows with offsets: whole tiles, diagonal tiles, a far key that stands out."""
+    g = torch.Generator().manual_seed(9)
+    segs = [(0, 300), (517, 260), (64, 129), (1000, 2)]
+    meta = make_meta(page, segs, 400, seed=3)
+    q = torch.randn(meta.num_tokens, H * D, generator=g).to(torch.bfloat16).to(DEV)
+    kc = torch.randn(401, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    vc = torch.randn(401, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    kc[meta.block_table[1, 3].long(), :, 5, :] *= 3.0
+    want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+    for tc in (True, False):
+        ops.tc_attention = tc
+        try:
+            got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+        finally:
+            ops.tc_attention = True
+        ops.check_errors()
+        close(got, want, torch.bfloat16)
 
 
 def test_sampling(ops):
