@@ -191,7 +191,7 @@ def profile(args, cfg, torch, LLM):
     from mini_inference_b200.engine.batch import StepEntry
     from mini_inference_b200.engine.graphs import DecodeGraphs
     vocab = cfg["vocab_size"]
-    llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
+    llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=args.page_size,
               kv_cache_tokens=args.batch * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=args.batch,
               max_model_len=args.ctx, max_batched_tokens=4096, cuda_graphs=False)
     if args.profile == "prefill":
@@ -235,6 +235,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run only a few decode steps (cache filled without a prefill) or one prefill, for ncu")
     args = ap.parse_args()

@@ -68,9 +68,10 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, c = lane & 3;
-    const int tile = gridDim.x - 1 - blockIdx.x;   // later tiles see more keys: start them first
+    // blocks are handed out x-fastest: all heads of the last (longest) tile first, then the tile before it ...
+    const int tile = gridDim.y - 1 - blockIdx.y;
     const int seg = tiles[2 * tile], r0 = tiles[2 * tile + 1];
-    const int h = blockIdx.y, kvh = h / (H / KV);
+    const int h = blockIdx.x, kvh = h / (H / KV);
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
     const int rows = min(BQ, n - r0);
     const int* table_row = block_table + (size_t)seg * table_stride;
@@ -218,7 +219,7 @@ MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cac
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
     const size_t smem = (size_t)4 * BK * D * 2;
-    dim3 grid(num_tiles, H);
+    dim3 grid(H, num_tiles);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD, IDX) do { \
         if (!configured[IDX]) { \

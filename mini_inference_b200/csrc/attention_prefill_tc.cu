@@ -41,21 +41,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                        int H, int KV, int ps, float scale_log2, int window, int* __restrict__ error_word) {
     constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a head
     constexpr int Q_BYTES = BQ * D * 2, KV_BYTES = BKV * D * 2;
-    constexpr int TMEM_COLS = 256;                       // S: 64, P: 32, O: D (<= 128)
-    constexpr uint32_t S_COL = 0, P_COL = 64, O_COL = 128;
+    constexpr int TMEM_COLS = 256;                       // S0: 64, S1: 64 (P overwrites the first 32 columns of its S), O: D
+    constexpr uint32_t S_COL = 0, O_COL = 128;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // [Q][K0][K1][V0][V1][barriers]
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + Q_BYTES + 4 * KV_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     const uint32_t sQ = smem_u32(base), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES;
     const uint32_t q_full = smem_u32(bars), kv_full = smem_u32(bars + 1), kv_empty = smem_u32(bars + 3),
-                   s_full = smem_u32(bars + 5), p_ready = smem_u32(bars + 6), o_done = smem_u32(bars + 7);
+                   s_full = smem_u32(bars + 5), p_ready = smem_u32(bars + 7), pv_done = smem_u32(bars + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int tile = gridDim.x - 1 - blockIdx.x;         // later tiles see more keys: start them first
+    // blocks are handed out x-fastest: all heads of the last (longest) tile first, then the tile before it ...
+    const int tile = gridDim.y - 1 - blockIdx.y;
     const int seg = tiles[2 * tile], r0 = tiles[2 * tile + 1];
-    const int h = blockIdx.y, kvh = h / (H / KV);
+    const int h = blockIdx.x, kvh = h / (H / KV);
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
     const int rows = min(BQ, n - r0);
     const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
@@ -67,7 +68,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         mbar_init(q_full, 1);
         mbar_init(kv_full, 1); mbar_init(kv_full + 8, 1);
         mbar_init(kv_empty, 1); mbar_init(kv_empty + 8, 1);
-        mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+        mbar_init(s_full, 1); mbar_init(s_full + 8, 1); mbar_init(p_ready, 128); mbar_init(pv_done, 1);
         mbar_init_fence();
         tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
     }
@@ -80,29 +81,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     pdl_wait();
 
     if (warp == 0) {
-        // ---------------- loads
+        // ---------------- loads.  Lane 0 owns the barriers; the page boxes of a tile (pages x column
+        // blocks x {K, V}, at most 32) are issued by one lane each, so the block-table look-ups and
+        // the TMA issue latencies of a tile overlap instead of queueing behind one thread.
         if (lane == 0) {
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
             for (int hb = 0; hb < HALVES; ++hb)
                 tma_load_2d(sQ + hb * (BQ * 128), &qmap, h * D + hb * 64, qs + r0, q_full);
-            const int* table_row = block_table + (size_t)seg * table_stride;
-            const int pages_per_tile = BKV / ps;
-            for (int i = 0; i < nt; ++i) {
-                const int s = i & 1, kt = kt_lo + i;
-                if (i >= 2 && !mbar_wait(kv_empty + 8 * s, ((i >> 1) - 1) & 1)) { atomicExch(error_word, 21); break; }
-                mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
-                for (int pg = 0; pg < pages_per_tile; ++pg) {
-                    const int j = kt * BKV + pg * ps;
-                    const int page = j <= p_last ? table_row[j / ps] : 0;          // beyond the last row's keys: null page
-                    const int y = (page * KV + kvh) * ps;
-#pragma unroll
-                    for (int hb = 0; hb < HALVES; ++hb) {
-                        const uint32_t off = s * KV_BYTES + hb * (BKV * 128) + pg * ps * 128;
-                        tma_load_2d(sK + off, &kmap, hb * 64, y, kv_full + 8 * s);
-                        tma_load_2d(sV + off, &vmap, hb * 64, y, kv_full + 8 * s);
-                    }
-                }
+        }
+        const int* table_row = block_table + (size_t)seg * table_stride;
+        const int pages_per_tile = BKV / ps;
+        const int ops_per_tile = pages_per_tile * HALVES * 2;
+        bool ok = true;
+        for (int i = 0; i < nt; ++i) {
+            const int s = i & 1, kt = kt_lo + i;
+            if (lane == 0) {
+                if (i >= 2 && !mbar_wait(kv_empty + 8 * s, ((i >> 1) - 1) & 1)) { atomicExch(error_word, 21); ok = false; }
+                if (ok) mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            for (int op = lane; op < ops_per_tile; op += 32) {
+                const int pg = op / (HALVES * 2), hb = (op / 2) % HALVES, is_v = op & 1;
+                const int j = kt * BKV + pg * ps;
+                const int page = j <= p_last ? table_row[j / ps] : 0;              // beyond the last row's keys: null page
+                const int y = (page * KV + kvh) * ps;
+                const uint32_t off = s * KV_BYTES + hb * (BKV * 128) + pg * ps * 128;
+                tma_load_2d((is_v ? sV : sK) + off, is_v ? &vmap : &kmap, hb * 64, y, kv_full + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -114,29 +120,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (!ok) atomicExch(error_word, 22);
             auto issue_qk = [&](int i) {
                 const int s = i & 1;
-                if (!mbar_wait(kv_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 23); ok = false; return; }
+                if (!mbar_spin(kv_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 23); ok = false; return; }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t a = sQ + (ks / 4) * (BQ * 128) + (ks % 4) * 32;
                     const uint32_t b = sK + s * KV_BYTES + (ks / 4) * (BKV * 128) + (ks % 4) * 32;
-                    umma_ss(tmem + S_COL, umma_desc_sw128(a, 16, 1024), umma_desc_sw128(b, 16, 1024), idesc_s, ks != 0);
+                    umma_ss(tmem + S_COL + 64 * s, umma_desc_sw128(a, 16, 1024), umma_desc_sw128(b, 16, 1024), idesc_s, ks != 0);
                 }
-                umma_commit(s_full);
+                umma_commit(s_full + 8 * s);
             };
+            // The scores of tile i+1 are issued BEFORE waiting for the softmax of tile i, into the other
+            // S buffer, so the tensor cores work while the softmax warps do.
             if (ok) issue_qk(0);
             for (int i = 0; i < nt && ok; ++i) {
                 const int s = i & 1;
-                if (!mbar_wait(p_ready, i & 1)) { atomicExch(error_word, 24); ok = false; break; }
+                if (i + 1 < nt) issue_qk(i + 1);
+                if (!ok) break;
+                if (!mbar_spin(p_ready, i & 1)) { atomicExch(error_word, 24); ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
                     const uint32_t b = sV + s * KV_BYTES + kk * (16 * 128);
-                    umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, umma_desc_sw128(b, BKV * 128, 1024), idesc_o, (i | kk) != 0);
+                    umma_ts(tmem + O_COL, tmem + S_COL + 64 * s + kk * 8, umma_desc_sw128(b, BKV * 128, 1024), idesc_o, (i | kk) != 0);
                 }
                 umma_commit(kv_empty + 8 * s);                 // K and V of this stage are free once these finish
-                if (i + 1 < nt) issue_qk(i + 1);
-                else umma_commit(o_done);
+                umma_commit(pv_done);                          // and O holds tile i
             }
         }
     } else {
@@ -149,11 +158,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         bool ok = true;
         for (int i = 0; i < nt && ok; ++i) {
             const int kt = kt_lo + i;
-            if (!mbar_wait(s_full, i & 1)) { atomicExch(error_word, 25); ok = false; break; }
+            const uint32_t s_col = S_COL + 64 * (i & 1);
+            if (!mbar_spin(s_full + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(error_word, 25); ok = false; break; }
             tc_fence_after();
             uint32_t r[64];                                     // the row's 64 scores, scaled and masked in place
-            tmem_ld32(lane_addr + S_COL, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-            tmem_ld32(lane_addr + S_COL + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tmem_ld32(lane_addr + s_col, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld32(lane_addr + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
             tmem_wait_ld();
             float mx = -INFINITY;
             const bool inside = kt * BKV + BKV - 1 <= p_row && (window <= 0 || kt * BKV > p_row - window);
@@ -180,14 +190,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const float p0 = exp2f(__uint_as_float(r[2 * c]) - off), p1 = exp2f(__uint_as_float(r[2 * c + 1]) - off);
+                const float p0 = fast_exp2(__uint_as_float(r[2 * c]) - off), p1 = fast_exp2(__uint_as_float(r[2 * c + 1]) - off);
                 sum += p0 + p1;
                 __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                 pk[c] = *reinterpret_cast<uint32_t*>(&hh);
             }
             l += sum;
-            tmem_st32(lane_addr + P_COL, pk);
-            if (__any_sync(0xffffffffu, rescale)) {            // the previous O += P V is complete (s_full implies it)
+            tmem_st32(lane_addr + s_col, pk);                  // P takes the place of the scores it came from
+            // Every thread follows pv_done phase by phase (a parity wait can only tell the current phase
+            // from the one before it); O holds tile i-1 completely after this.
+            if (i > 0 && !mbar_spin(pv_done, (i - 1) & 1)) { atomicExch(error_word, 27); ok = false; }
+            if (__any_sync(0xffffffffu, rescale)) {
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
@@ -203,7 +217,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             mbar_arrive(p_ready);
         }
         // ---------------- epilogue
-        if (ok && !mbar_wait(o_done, 0)) { atomicExch(error_word, 26); ok = false; }
+        if (ok && !mbar_wait(pv_done, (nt - 1) & 1)) { atomicExch(error_word, 26); ok = false; }
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -263,9 +277,9 @@ MI_EXPORT int mi_attn_prefill_tc(const void* q, int q_stride, int num_tokens, co
     CUtensorMap qmap, kmap, vmap;
     if (!sm100_host::make_map_bf16(&qmap, q, num_tokens, (uint64_t)H * D, q_stride, BQ, 64)) return -5;
     if (!cache_map(k_cache, cache_rows, D, ps, &kmap) || !cache_map(v_cache, cache_rows, D, ps, &vmap)) return -5;
-    const size_t smem = (size_t)BQ * D * 2 + 4 * (size_t)BKV * D * 2 + 8 * 8 + 16 + 1024;
+    const size_t smem = (size_t)BQ * D * 2 + 4 * (size_t)BKV * D * 2 + 9 * 8 + 16 + 1024;
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(num_tiles, H);
+    dim3 grid(H, num_tiles);
 #define LAUNCH(DD, IDX) do { \
         static bool configured = false; \
         if (!configured) { \

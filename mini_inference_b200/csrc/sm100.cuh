@@ -10,7 +10,7 @@
 namespace mi {
 namespace sm100 {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 22;      // bounded waits: about a quarter of a second, then give up
+constexpr uint32_t SPIN_LIMIT = 1u << 20;      // bounded waits: this many parked attempts, then give up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -28,19 +28,33 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;      // try_wait parks the thread for a bounded, implementation-defined time before answering
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 // false when the phase did not complete within the limit (the caller records an error and moves on)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 128) __nanosleep(32);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+        if (mbar_try(bar, parity)) return true;
+    return false;
+}
+
+// spinning variant for waits that are expected to be short (a bounded number of polls, no parking)
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (SPIN_LIMIT << 6); ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
     }
     return false;
+}
+__device__ __forceinline__ float fast_exp2(float x) {      // ex2.approx: 2 ulp, exp2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // ------------------------------------------------------------------ TMA (no cluster multicast anywhere)
