@@ -198,6 +198,7 @@ def profile(args, cfg, torch, LLM):
         ms = prefill(llm, torch, 2048, vocab, warmup=1, reps=args.steps)
         print(f"prefill 2048 tokens: {ms:.3f} ms")
         return 0
+    llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32})
     llm.graphs = DecodeGraphs(llm.runner, args.batch, buckets=[args.batch])
     llm.graphs.capture()
     seqs = []

@@ -61,6 +61,8 @@ def bench_gemm(args, ops, peak):
                          cfg["intermediate_size"], cfg["vocab_size"])
     shapes = [("qkv", (H + 2 * KV) * D, h), ("o", h, H * D), ("gate_up", 2 * I, h), ("down", h, I), ("lm_head", V, h)]
     for name, N, K in shapes:
+        if args.only and name not in args.only:
+            continue
         copies = max(2, -(-args.rotate_mb * 2 ** 20 // (N * K * 2)))      # rotate >= rotate_mb of weights
         ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
         for M in args.rows:
@@ -117,6 +119,7 @@ def main(argv=None):
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--batch", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--only", default=None, type=lambda s: s.split(","), help="gemm: only these (qkv,o,gate_up,down,lm_head)")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--rotate-mb", type=int, default=512, help="rotate through at least this many MB of operands")
