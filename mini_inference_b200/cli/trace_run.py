@@ -78,6 +78,8 @@ def main(argv=None) -> int:
             if seq is not None:
                 runner.cache.free(seq)
         print(f"done {step}", flush=True)
+    if hasattr(runner.ops, "check_errors"):
+        runner.ops.check_errors()
     return 0
 
 

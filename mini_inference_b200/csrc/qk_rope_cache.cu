@@ -5,7 +5,8 @@
 // engine/core/kv_cache.py:378-382 (the write, before attention).  The reference runs this
 // as ~15 elementwise kernels and two index copies.
 //
-// One warp per (token, head); a block holds 4 consecutive heads of one token.  Each lane computes
+// One warp per (token, head) item; warps walk the items with a grid-wide stride, so a long prompt
+// costs a few hundred blocks instead of one tiny block per four heads.  Each lane computes
 // cos/sin of pos * inv_freq[i] in float32 for the pairs (i, i + D/2) it rotates.  q is rotated in
 // place inside the qkv buffer; k (rotated) and v go to cache position `slot` of their kv head:
 //   cache[(page * KV + head) * page_size + offset][0..D)   with page = slot / page_size.
@@ -19,14 +20,16 @@ template <typename T, typename WT>
 __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restrict__ q_w, const WT* __restrict__ k_w,
                                           const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                          int H, int KV, int D, int page_size, float eps) {
+                                          int H, int KV, int D, int page_size, float eps, int num_tokens) {
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
-    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (h >= H + 2 * KV) return;
+    const int heads = H + 2 * KV;
     const int half = D / 2;
+    const long long items = (long long)num_tokens * heads;
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < items; item += stride) {
+    const int t = (int)(item / heads), h = (int)(item % heads);
     // heads 0..H-1 are q, H..H+KV-1 are k, H+KV..H+2KV-1 are v
     T* x = qkv + ((size_t)t * (H + 2 * KV) + h) * D;
     size_t cache_base = 0;
@@ -45,10 +48,10 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restr
                 for (int i = lane; i < D; i += 32) dst[i] = x[i];
             }
         }
-        return;
+        continue;
     }
     const bool is_k = h >= H;
-    if (is_k && !k_cache) return;                          // reads another step's cache: k unused
+    if (is_k && !k_cache) continue;                          // reads another step's cache: k unused
     const WT* w = is_k ? k_w : q_w;
     // each lane takes PAIRS of neighbouring elements (one 4- or 8-byte access) of both halves
     float ss = 0.f;
@@ -84,6 +87,7 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, const WT* __restr
         store2(dst + i + half, o2[0], o2[1]);
     }
 }
+}
 
 MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w, const float* inv_freq,
                                     const int* positions, const int* slots, void* k_cache, void* v_cache,
@@ -91,8 +95,10 @@ MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w,
                                     cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (D % 4 || D / 2 > MAX_HALF) return -2;
-#define LAUNCH(T, WT) return (int)launch_pdl(qk_norm_rope_cache_kernel<T, WT>, dim3(T_, (H + 2 * KV + 3) / 4), dim3(128), 0, stream, (T*)qkv, (const WT*)q_w, (const WT*)k_w, \
-        inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, D, page_size, eps)
+    const long long items = (long long)T_ * (H + 2 * KV);
+    const int blocks = (int)((items + 7) / 8 < 148 * 8 ? (items + 7) / 8 : 148 * 8);
+#define LAUNCH(T, WT) return (int)launch_pdl(qk_norm_rope_cache_kernel<T, WT>, dim3(blocks), dim3(256), 0, stream, (T*)qkv, (const WT*)q_w, (const WT*)k_w, \
+        inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, D, page_size, eps, T_)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);
     else if (w_dtype == MI_F32) LAUNCH(float, float);

@@ -193,6 +193,8 @@ class LLM:
         for r in reqs:
             if r.error:
                 raise RuntimeError(f"request {r.id} failed: {r.error}")
+        if hasattr(self.ops, "check_errors"):
+            self.ops.check_errors()                    # a bounded wait inside a kernel ran out: the tokens cannot be trusted
         return [list(r.output_ids) for r in reqs]
 
     def score(self, token_ids: Sequence[int]) -> torch.Tensor:

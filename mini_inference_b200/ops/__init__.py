@@ -162,7 +162,7 @@ class CudaOps:
                 return b
         return 0
 
-    def tune_linear(self, weights, out_dtypes=None, iters=16):
+    def tune_linear(self, weights, out_dtypes=None, iters=16, min_bytes=256 << 20):
         """Per weight shape and row-count bucket, time this package's few-row kernels against the
         library GEMM on the model's own weights and remember the fastest.  The reference does the
         same kind of start-up timing to choose a weight layout per shape
@@ -179,7 +179,7 @@ class CudaOps:
             for (N, K), ws in groups.items():
                 od = (out_dtypes or {}).get((N, K))
                 # one weight cannot defeat the L2 by rotation; leave such shapes to the default rule
-                if len(ws) * N * K * 2 < (256 << 20) and N * K * 2 < (256 << 20):
+                if len(ws) * N * K * 2 < min_bytes:
                     continue
                 for M in self.ROW_BUCKETS:
                     x = torch.randn(M, K, device=ws[0].device, dtype=torch.bfloat16)

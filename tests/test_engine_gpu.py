@@ -86,3 +86,39 @@ def test_preemption_on_gpu(tiny_dirs):
     llm = LLM(d, dtype="float32", device=DEV, kv_block_size=8, kv_cache_tokens=48, kv_watermark=0.0, cuda_graphs=True)
     assert llm.generate(prompts, SamplingParams(max_new_tokens=20)) == want
     assert llm.stats()["preemptions"] > 0
+
+
+def test_linear_tuning_table():
+    """The start-up timing fills a table per (row bucket, shape) and the chosen kernels still compute the product."""
+    from mini_inference_b200.ops import get_ops
+    ops = get_ops(DEV)
+    g = torch.Generator().manual_seed(0)
+    ws = [(torch.randn(512, 256, generator=g) * 0.05).to(torch.bfloat16).to(DEV) for _ in range(3)]
+    saved = ops._linear_choice
+    try:
+        report = ops.tune_linear(ws, iters=4, min_bytes=0)
+        assert set(ops._linear_choice) == {(m, 512, 256) for m in ops.ROW_BUCKETS}
+        assert all(v["best"] in ("library", "stream", "skinny") for v in report.values())
+        x = torch.randn(5, 256, generator=g).to(torch.bfloat16).to(DEV)
+        want = x.float() @ ws[0].float().T
+        got = ops.linear(x, ws[0], out_dtype=torch.float32)
+        assert ((got - want).abs().max() / want.abs().max()).item() < 1e-4
+    finally:
+        ops._linear_choice = saved
+
+
+def test_run_engine_command_line(tmp_path):
+    import json
+    import os
+    import subprocess
+    from tests.conftest import ROOT
+    out = tmp_path / "r.json"
+    r = subprocess.run([os.path.join(ROOT, "bin", "run_engine"), "--random-weights", "tiny", "-n", "5", "-c", "3", "--warmup", "1",
+                        "--max-new-tokens", "12", "--prompt-len", "3:20", "--kv-tokens", "512", "--cuda-graphs", "on",
+                        "--chunked-prefill", "on", "--max-batched-tokens", "16", "--temperature", "0.7", "--out", str(out)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    data = json.loads(out.read_text())
+    assert data["summary"]["num_prompts"] == 5 and len(data["runs"]) == 5
+    assert all(run["generated_tokens"] == 12 and run["error"] is None for run in data["runs"])
+    assert data["summary"]["throughput_tok_s"] > 0 and data["summary"]["graph_replays"] > 0
