@@ -27,10 +27,25 @@
 using namespace mi;
 using namespace mi::sm100;
 
+#ifdef MI_ATT_TIMING
+// phase counters (clock64 ticks summed over blocks): built only with -DMI_ATT_TIMING, read by mi_attn_tc_timing
+__device__ unsigned long long att_ticks[16];
+#define TICK(var) const long long var = clock64()
+#define ADD(slot, a, b) atomicAdd(&att_ticks[slot], (unsigned long long)((b) - (a)))
+MI_EXPORT int mi_attn_tc_timing(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, att_ticks, sizeof(att_ticks));
+    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(att_ticks, z, sizeof(z)); }
+    return (int)e;
+}
+#else
+#define TICK(var)
+#define ADD(slot, a, b)
+#endif
+
 namespace {
 
 constexpr int BQ = 128, BKV = 64;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 224;      // warp 0: Q and K loads, 1: MMA issue, 2-5: softmax, 6: V loads
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
@@ -47,10 +62,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // [Q][K0][K1][V0][V1][barriers]
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + Q_BYTES + 4 * KV_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     const uint32_t sQ = smem_u32(base), sK = sQ + Q_BYTES, sV = sK + 2 * KV_BYTES;
-    const uint32_t q_full = smem_u32(bars), kv_full = smem_u32(bars + 1), kv_empty = smem_u32(bars + 3),
-                   s_full = smem_u32(bars + 5), p_ready = smem_u32(bars + 7), pv_done = smem_u32(bars + 8);
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), k_empty = smem_u32(bars + 3),
+                   s_full = smem_u32(bars + 5), p_ready = smem_u32(bars + 7), pv_done = smem_u32(bars + 8),
+                   v_full = smem_u32(bars + 9), v_empty = smem_u32(bars + 11);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // blocks are handed out x-fastest: all heads of the last (longest) tile first, then the tile before it ...
@@ -66,8 +82,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        mbar_init(kv_full, 1); mbar_init(kv_full + 8, 1);
-        mbar_init(kv_empty, 1); mbar_init(kv_empty + 8, 1);
+        mbar_init(k_full, 1); mbar_init(k_full + 8, 1); mbar_init(k_empty, 1); mbar_init(k_empty + 8, 1);
+        mbar_init(v_full, 1); mbar_init(v_full + 8, 1); mbar_init(v_empty, 1); mbar_init(v_empty + 8, 1);
         mbar_init(s_full, 1); mbar_init(s_full + 8, 1); mbar_init(p_ready, 128); mbar_init(pv_done, 1);
         mbar_init_fence();
         tma_prefetch_desc(&qmap); tma_prefetch_desc(&kmap); tma_prefetch_desc(&vmap);
@@ -80,11 +96,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
     pdl_trigger();
     pdl_wait();
 
-    if (warp == 0) {
-        // ---------------- loads.  Lane 0 owns the barriers; the page boxes of a tile (pages x column
-        // blocks x {K, V}, at most 32) are issued by one lane each, so the block-table look-ups and
-        // the TMA issue latencies of a tile overlap instead of queueing behind one thread.
-        if (lane == 0) {
+    if (warp == 0 || warp == 6) {
+        // ---------------- loads.  Warp 0 brings the query tile and the key tiles, warp 6 the value tiles, each
+        // through its own two-stage ring: a key stage is free as soon as its QK^T has run, a value stage only
+        // after P V, so keys run further ahead.  Lane 0 owns the barriers; the page boxes of a tile are issued
+        // by one lane each, so block-table look-ups and TMA issue latencies overlap.
+        const bool is_v = warp == 6;
+        if (!is_v && lane == 0) {
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
             for (int hb = 0; hb < HALVES; ++hb)
@@ -92,23 +110,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         }
         const int* table_row = block_table + (size_t)seg * table_stride;
         const int pages_per_tile = BKV / ps;
-        const int ops_per_tile = pages_per_tile * HALVES * 2;
+        const int ops_per_tile = pages_per_tile * HALVES;
+        const uint32_t full = is_v ? v_full : k_full, empty = is_v ? v_empty : k_empty, dst0 = is_v ? sV : sK;
+        const CUtensorMap* map = is_v ? &vmap : &kmap;
         bool ok = true;
         for (int i = 0; i < nt; ++i) {
             const int s = i & 1, kt = kt_lo + i;
             if (lane == 0) {
-                if (i >= 2 && !mbar_wait(kv_empty + 8 * s, ((i >> 1) - 1) & 1)) { atomicExch(error_word, 21); ok = false; }
-                if (ok) mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
+                if (i >= 2 && !mbar_wait(empty + 8 * s, ((i >> 1) - 1) & 1)) { atomicExch(error_word, 21); ok = false; }
+                if (ok) mbar_expect_tx(full + 8 * s, KV_BYTES);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             for (int op = lane; op < ops_per_tile; op += 32) {
-                const int pg = op / (HALVES * 2), hb = (op / 2) % HALVES, is_v = op & 1;
+                const int pg = op / HALVES, hb = op % HALVES;
                 const int j = kt * BKV + pg * ps;
                 const int page = j <= p_last ? table_row[j / ps] : 0;              // beyond the last row's keys: null page
                 const int y = (page * KV + kvh) * ps;
-                const uint32_t off = s * KV_BYTES + hb * (BKV * 128) + pg * ps * 128;
-                tma_load_2d((is_v ? sV : sK) + off, is_v ? &vmap : &kmap, hb * 64, y, kv_full + 8 * s);
+                tma_load_2d(dst0 + s * KV_BYTES + hb * (BKV * 128) + pg * ps * 128, map, hb * 64, y, full + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -120,7 +139,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (!ok) atomicExch(error_word, 22);
             auto issue_qk = [&](int i) {
                 const int s = i & 1;
-                if (!mbar_spin(kv_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 23); ok = false; return; }
+                if (!mbar_spin(k_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 23); ok = false; return; }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -128,6 +147,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     const uint32_t b = sK + s * KV_BYTES + (ks / 4) * (BKV * 128) + (ks % 4) * 32;
                     umma_ss(tmem + S_COL + 64 * s, umma_desc_sw128(a, 16, 1024), umma_desc_sw128(b, 16, 1024), idesc_s, ks != 0);
                 }
+                umma_commit(k_empty + 8 * s);                  // the keys of this stage are free once these finish
                 umma_commit(s_full + 8 * s);
             };
             // The scores of tile i+1 are issued BEFORE waiting for the softmax of tile i, into the other
@@ -135,20 +155,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             if (ok) issue_qk(0);
             for (int i = 0; i < nt && ok; ++i) {
                 const int s = i & 1;
+                TICK(m0);
                 if (i + 1 < nt) issue_qk(i + 1);
                 if (!ok) break;
+                TICK(m1);
                 if (!mbar_spin(p_ready, i & 1)) { atomicExch(error_word, 24); ok = false; break; }
+                TICK(m2);
+                if (!mbar_spin(v_full + 8 * s, (i >> 1) & 1)) { atomicExch(error_word, 28); ok = false; break; }
+                TICK(m3);
+                ADD(4, m0, m1); ADD(5, m1, m2); ADD(6, m2, m3);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
                     const uint32_t b = sV + s * KV_BYTES + kk * (16 * 128);
                     umma_ts(tmem + O_COL, tmem + S_COL + 64 * s + kk * 8, umma_desc_sw128(b, BKV * 128, 1024), idesc_o, (i | kk) != 0);
                 }
-                umma_commit(kv_empty + 8 * s);                 // K and V of this stage are free once these finish
+                umma_commit(v_empty + 8 * s);                  // the values of this stage are free once these finish
                 umma_commit(pv_done);                          // and O holds tile i
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------- softmax: thread <-> query row <-> tensor-memory lane
         const int lg = warp & 3;
         const int row = lg * 32 + lane;                        // row of the tile
@@ -159,44 +185,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         for (int i = 0; i < nt && ok; ++i) {
             const int kt = kt_lo + i;
             const uint32_t s_col = S_COL + 64 * (i & 1);
+            TICK(t0);
             if (!mbar_spin(s_full + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(error_word, 25); ok = false; break; }
             tc_fence_after();
+            TICK(t1);
             uint32_t r[64];                                     // the row's 64 scores, scaled and masked in place
             tmem_ld32(lane_addr + s_col, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
             tmem_ld32(lane_addr + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
             tmem_wait_ld();
-            float mx = -INFINITY;
+            // Scores stay unscaled in r[]; the scale is folded into the exponent's multiply-add.  Only tiles
+            // that touch the diagonal (or the window's edge) for some row of the warp pay for masking.
             const bool inside = kt * BKV + BKV - 1 <= p_row && (window <= 0 || kt * BKV > p_row - window);
+            if (!__all_sync(0xffffffffu, inside)) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const float v = __uint_as_float(r[c]) * scale_log2;
-                const int j = kt * BKV + c;
-                const bool vis = inside || (j <= p_row && (window <= 0 || j > p_row - window));
-                const float sv = vis ? v : -INFINITY;
-                r[c] = __float_as_uint(sv);
-                mx = fmaxf(mx, sv);
+                for (int c = 0; c < 64; ++c) {
+                    const int j = kt * BKV + c;
+                    const bool vis = j <= p_row && (window <= 0 || j > p_row - window);
+                    if (!vis) r[c] = 0xff800000u;                     // -inf
+                }
             }
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one
+#pragma unroll
+            for (int c = 0; c < 64; ++c) mxs[c & 3] = fmaxf(mxs[c & 3], __uint_as_float(r[c]));
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;   // scale > 0
             // keep the exponent offset unless the maximum grew by more than 2^8: rescaling O is then rare
             float alpha = 1.f;
             bool rescale = false;
             if (mx > m_ref + 8.f) {
-                alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
                 rescale = i > 0 && m_ref != -INFINITY;
                 m_ref = mx;
                 l *= alpha;
             }
             const float off = m_ref == -INFINITY ? 0.f : m_ref;
             uint32_t pk[32];
-            float sum = 0.f;
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const float p0 = fast_exp2(__uint_as_float(r[2 * c]) - off), p1 = fast_exp2(__uint_as_float(r[2 * c + 1]) - off);
-                sum += p0 + p1;
+                const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * c]), scale_log2, -off));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * c + 1]), scale_log2, -off));
+                sums[c & 3] += p0 + p1;
                 __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                 pk[c] = *reinterpret_cast<uint32_t*>(&hh);
             }
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l += sum;
             tmem_st32(lane_addr + s_col, pk);                  // P takes the place of the scores it came from
+            TICK(t2);
             // Every thread follows pv_done phase by phase (a parity wait can only tell the current phase
             // from the one before it); O holds tile i-1 completely after this.
             if (i > 0 && !mbar_spin(pv_done, (i - 1) & 1)) { atomicExch(error_word, 27); ok = false; }
@@ -215,6 +250,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(p_ready);
+            TICK(t3);
+#ifdef MI_ATT_TIMING
+            if (threadIdx.x == 64) { ADD(0, t0, t1); ADD(1, t1, t2); ADD(2, t2, t3); atomicAdd(&att_ticks[3], 1ull); }
+#endif
         }
         // ---------------- epilogue
         if (ok && !mbar_wait(pv_done, (nt - 1) & 1)) { atomicExch(error_word, 26); ok = false; }
@@ -277,7 +316,7 @@ MI_EXPORT int mi_attn_prefill_tc(const void* q, int q_stride, int num_tokens, co
     CUtensorMap qmap, kmap, vmap;
     if (!sm100_host::make_map_bf16(&qmap, q, num_tokens, (uint64_t)H * D, q_stride, BQ, 64)) return -5;
     if (!cache_map(k_cache, cache_rows, D, ps, &kmap) || !cache_map(v_cache, cache_rows, D, ps, &vmap)) return -5;
-    const size_t smem = (size_t)BQ * D * 2 + 4 * (size_t)BKV * D * 2 + 9 * 8 + 16 + 1024;
+    const size_t smem = (size_t)BQ * D * 2 + 4 * (size_t)BKV * D * 2 + 13 * 8 + 16 + 1024;
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(H, num_tiles);
 #define LAUNCH(DD, IDX) do { \

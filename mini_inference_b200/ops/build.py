@@ -32,6 +32,7 @@ BUILD = os.path.join(_out_dir(), "_build")
 LIB = os.path.join(_out_dir(), "_kernels.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+NVCC_FLAGS += os.environ.get("MI_NVCC_EXTRA", "").split()        # e.g. -DMI_ATT_TIMING for the kernels' phase counters
 
 
 def _nvcc() -> str:
