@@ -266,10 +266,10 @@ def main():
               max_batched_tokens=4096, cuda_graphs=True)
 
     with ClockSampler() as clocks:
+        pre_ms = prefill(llm, torch, 2048, vocab, warmup=3, reps=5)
         main_run = decode_device(llm, torch, args.batch, args.ctx, args.steps, args.warmup, vocab)
         clock_summary = clocks.summary(*main_run["t"])
         e2e = decode_e2e(llm, torch, args.batch, args.ctx, args.steps, args.warmup, vocab)
-        pre_ms = prefill(llm, torch, 2048, vocab)
         points = {}
         if not args.skip_points:
             for b in (1, 64):
