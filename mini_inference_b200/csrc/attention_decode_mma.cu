@@ -19,7 +19,7 @@
 // (max, sum, output); the warps are merged through shared memory at the end, the splits by
 // mi_attn_decode_merge (attention_generic.cu) when there is more than one.
 // Needs page_size % 16 == 0 (a 16-key block never straddles a page) and G <= 16.
-#include "common.cuh"
+#include "sm100.cuh"
 #include <math.h>
 
 using namespace mi;
@@ -43,14 +43,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 constexpr int DEC_WARPS = 4;
 
-template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 3)
+constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per warp
+
+// BULK = false: K/V go from the pages straight into registers (one block ahead).
+// BULK = true:  each warp keeps a ring of DEC_STAGES (K tile, V tile) pairs in shared memory, filled by
+//               cp.async.bulk (one 16-key x D tile of a page and kv head is contiguous in the cache), signalled
+//               by per-warp mbarriers; fragments are then read from shared memory.  More bytes in flight per SM
+//               at no register cost.
+template <int D, bool BULK>
+__global__ void __launch_bounds__(DEC_WARPS * 32, BULK ? 2 : 3)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
-                       float scale_log2, int window, int* __restrict__ merge_counters) {
+                       float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word) {
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
@@ -72,7 +79,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     // query fragments, permuted: the 16 bytes at d = 32 j + 8 c of rows g and g + 8.  They are the
     // same for all warps and live in shared memory ([k-step][lane] x 16 bytes) to keep registers
     // for the loads in flight.
-    uint4* q_frag = reinterpret_cast<uint4*>(smem + DEC_WARPS * 16 * (D + 2));
+    constexpr int TILE = 16 * D * 2;                                     // bytes of one K or V tile
+    constexpr int MERGE_BYTES = DEC_WARPS * 16 * (D + 2) * 4;
+    constexpr int RING_BYTES = BULK ? DEC_WARPS * DEC_STAGES * 2 * TILE : 0;
+    constexpr int FRONT = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;   // the merge scratch re-uses the ring
+    unsigned char* smem_bytes = reinterpret_cast<unsigned char*>(smem);
+    uint4* q_frag = reinterpret_cast<uint4*>(smem_bytes + FRONT);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bytes + FRONT + (D / 16) * 32 * 16);
+    unsigned char* ring = smem_bytes + warp * (DEC_STAGES * 2 * TILE);
+    const uint32_t bar0 = sm100::smem_u32(bars + warp * DEC_STAGES);
+    if (BULK && lane == 0) {
+        for (int st = 0; st < DEC_STAGES; ++st) sm100::mbar_init(bar0 + 8 * st, 1);
+        sm100::mbar_init_fence();
+    }
     if (warp == 0) {
         const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
 #pragma unroll
@@ -92,21 +111,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows g and g + 8; sums are per thread
 
     uint4 kreg[2][KS / 2];
-    auto load_k = [&](int blk) {
-        const int page = table_row[(blk * 16) / ps];
-        const __nv_bfloat16* base = k_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+    uint4 vreg[4][HALVES];
+    // fragments of one 16-key block: keys nt*8+g at d = 32 j + 8 c; values of keys 2c, 2c+1, 2c+8, 2c+9 at d = 64 hb + 8 g
+    auto frag_k = [&](const __nv_bfloat16* base) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int j = 0; j < KS / 2; ++j)
                 kreg[nt][j] = *reinterpret_cast<const uint4*>(base + (size_t)(nt * 8 + g) * D + 32 * j + 8 * c);
     };
-
-    // values of a block: rows of keys 2c, 2c+1, 2c+8, 2c+9, 16 bytes at d = 64 hb + 8 g
-    uint4 vreg[4][HALVES];
-    auto load_v = [&](int blk) {
-        const int page = table_row[(blk * 16) / ps];
-        const __nv_bfloat16* base = v_cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+    auto frag_v = [&](const __nv_bfloat16* base) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = 2 * c + (i & 1) + 8 * (i >> 1);
@@ -115,12 +129,44 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 vreg[i][hb] = *reinterpret_cast<const uint4*>(base + (size_t)key * D + 64 * hb + 8 * g);
         }
     };
+    auto tile_of = [&](const __nv_bfloat16* cache, int blk) {
+        const int page = table_row[(blk * 16) / ps];
+        return cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
+    };
+    auto load_k = [&](int blk) { frag_k(tile_of(k_cache, blk)); };
+    auto load_v = [&](int blk) { frag_v(tile_of(v_cache, blk)); };
+    // BULK: lane 0 asks for the K and V tiles of block `blk` into ring stage st
+    auto issue = [&](int blk, int st) {
+        if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            const uint32_t dst = sm100::smem_u32(ring + st * 2 * TILE), bar = bar0 + 8 * st;
+            sm100::mbar_expect_tx(bar, 2 * TILE);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                         :: "r"(dst), "l"(tile_of(k_cache, blk)), "r"(TILE), "r"(bar) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                         :: "r"(dst + TILE), "l"(tile_of(v_cache, blk)), "r"(TILE), "r"(bar) : "memory");
+        }
+    };
 
-    // Software pipeline: the keys of block i+1 are requested right after the scores of block i,
-    // the values of block i+1 right after block i's P*V, so each load has a whole iteration to land.
+    // Software pipeline.  Registers: the keys of block i+1 are requested right after the scores of block i,
+    // the values of block i+1 right after block i's P*V.  BULK: DEC_STAGES blocks are in flight in the ring;
+    // a block's fragments are copied to registers as soon as it lands and its stage is refilled at once.
     int blk = b0 + warp;
-    if (blk < b1) { load_k(blk); load_v(blk); }
-    for (; blk < b1; blk += DEC_WARPS) {
+    int nth = 0;
+    if (BULK) {
+        __syncwarp();
+        for (int st = 0; st < DEC_STAGES && blk + st * DEC_WARPS < b1; ++st) issue(blk + st * DEC_WARPS, st);
+    } else if (blk < b1) { load_k(blk); load_v(blk); }
+    for (; blk < b1; blk += DEC_WARPS, ++nth) {
+        if (BULK) {
+            const int st = nth % DEC_STAGES;
+            if (!sm100::mbar_wait(bar0 + 8 * st, (nth / DEC_STAGES) & 1)) { if (lane == 0) atomicExch(error_word, 31); break; }
+            const __nv_bfloat16* tile = reinterpret_cast<const __nv_bfloat16*>(ring + st * 2 * TILE);
+            frag_k(tile);
+            frag_v(tile + 16 * D);
+            __syncwarp();
+            if (blk + DEC_STAGES * DEC_WARPS < b1) issue(blk + DEC_STAGES * DEC_WARPS, st);
+        }
         // scores: 16 (heads) x 16 (keys) as two 8-key tiles
         float sc[2][4];
 #pragma unroll
@@ -133,7 +179,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 mma_bf16_16816(sc[nt], qa1, kreg[nt][j].z, kreg[nt][j].w);
             }
         }
-        if (blk + DEC_WARPS < b1) load_k(blk + DEC_WARPS);          // next block's keys fly during the rest
+        if (!BULK && blk + DEC_WARPS < b1) load_k(blk + DEC_WARPS);   // next block's keys fly during the rest
         // mask, online softmax (base 2)
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -183,8 +229,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 mma_bf16_16816(acc, pa, vb0, vb1);
             }
         }
-        if (blk + DEC_WARPS < b1) load_v(blk + DEC_WARPS);
+        if (!BULK && blk + DEC_WARPS < b1) load_v(blk + DEC_WARPS);
     }
+    if (BULK) __syncthreads();                    // every warp is done with its ring before the merge scratch overwrites it
 
     // row sums over the quad, then merge the warps
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -272,6 +319,11 @@ MI_EXPORT int mi_attn_decode_mma_fused(const void* q, int q_stride, const void* 
                                        const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                        int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                        int window, int* merge_counters, cudaStream_t stream);
+MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                      int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                      int window, int* merge_counters, int* error_word, cudaStream_t stream);
 
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
@@ -291,17 +343,39 @@ MI_EXPORT int mi_attn_decode_mma_fused(const void* q, int q_stride, const void* 
                                        const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                        int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                        int window, int* merge_counters, cudaStream_t stream) {
+    return mi_attn_decode_mma_bulk(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode,
+                                   seg_q_start, seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale,
+                                   window, merge_counters, nullptr, stream);
+}
+
+// error_word != null selects the variant that stages K/V through shared memory with cp.async.bulk and
+// per-warp mbarriers (bounded waits report through error_word); null keeps the register-streaming variant.
+MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                      int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                      int window, int* merge_counters, int* error_word, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
-    const size_t smem = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float) + (size_t)(D / 16) * 32 * 16;
+    const bool bulk = error_word != nullptr;
+    const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t ring_bytes = bulk ? (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 : 0;
+    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8;
     const float scale_log2 = scale * 1.4426950408889634f;
-#define LAUNCH(DD) do { \
-        return (int)launch_pdl(attn_decode_mma_kernel<DD>, grid, dim3(DEC_WARPS * 32), smem, stream, \
+#define LAUNCH(DD, BB) do { \
+        static bool configured = false; \
+        if (!configured && smem > 48 * 1024) { \
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+            configured = true; \
+        } \
+        return (int)launch_pdl(attn_decode_mma_kernel<DD, BB>, grid, dim3(DEC_WARPS * 32), smem, stream, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
-            H, KV, ps, scale_log2, window, merge_counters); } while (0)
-    if (D == 128) LAUNCH(128); else LAUNCH(64);
+            H, KV, ps, scale_log2, window, merge_counters, error_word); } while (0)
+    if (D == 128) { if (bulk) LAUNCH(128, true); else LAUNCH(128, false); }
+    else { if (bulk) LAUNCH(64, true); else LAUNCH(64, false); }
 #undef LAUNCH
     return (int)cudaGetLastError();
 }

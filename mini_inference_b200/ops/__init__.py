@@ -67,6 +67,9 @@ class CudaOps:
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
         self._sample_slots = self._sample_arrivals = None
+        # decode attention can stage K/V through shared memory with cp.async.bulk; measured slower than streaming
+        # them into registers (37 vs 33 us at batch 8, context 4096), so it is off unless asked for
+        self.bulk_decode = os.environ.get("MI_BULK_DECODE", "0") == "1"
         self.fused_merge = True              # the last split block to finish merges the splits (no merge launch)
         self._merge_counters = None
         self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
@@ -342,7 +345,7 @@ class CudaOps:
         fast_decode = fast and H // KV <= 16 and meta.page_size % 16 == 0
         if meta.num_decode:
             S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len,
-                                   3 if fast_decode else 2)
+                                   (2 if self.bulk_decode else 3) if fast_decode else 2)
             o_part = lse = None
             if S > 1:
                 o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)
@@ -354,10 +357,17 @@ class CudaOps:
                 if self._merge_counters is None or self._merge_counters.numel() < need:
                     self._merge_counters = torch.zeros(max(need, 8192), dtype=torch.int32, device=q.device)
                 counters = self._merge_counters
-            _check(self.lib.mi_attn_decode_mma_fused(
+            err_word = None
+            if self.bulk_decode:
+                if self._stream_error is None:
+                    self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
+                    self._stream_error = torch.zeros(1, dtype=torch.int32, device=q.device)
+                err_word = self._stream_error
+            _check(self.lib.mi_attn_decode_mma_bulk(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
-                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), self._stream()), "attn_decode_mma")
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), _p(err_word), self._stream()),
+                "attn_decode_mma")
             self.launches += 1
             if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,

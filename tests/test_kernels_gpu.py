@@ -230,11 +230,13 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
         for splits in (None, 1, 3):
             ops.force_splits, ops.fast_attention, ops.fused_merge = splits, fast, fused
             ops.tc_attention = splits != 3               # prompt portions: tcgen05 kernel, and the mma.sync kernel
+            ops.bulk_decode = splits != 1                # decoded tokens: bulk-copy ring, and register streaming
             try:
                 got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
                 got2 = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)    # counters were left clean
             finally:
                 ops.force_splits, ops.fast_attention, ops.fused_merge, ops.tc_attention = None, True, True, True
+                ops.bulk_decode = True
             close(got, want, dtype)
             assert torch.equal(got, got2)
             ops.check_errors()
