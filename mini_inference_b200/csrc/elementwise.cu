@@ -131,6 +131,50 @@ add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT*
     }
 }
 
+// Many rows: one WARP per row (shuffles only, no block barrier), 8 rows per block.
+template <typename T, typename WT, int VPT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
+                        const int* __restrict__ rows, int num_rows, int hidden, float eps) {
+    constexpr int V = Vec16<T>::N;
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= num_rows) return;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const int nvec = hidden / V;
+    float vals[VPT][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            load16(x + src + (size_t)i * V, vals[k]);
+            if (delta) {
+                float d[V];
+                load16(delta + src + (size_t)i * V, d);
+#pragma unroll
+                for (int e = 0; e < V; ++e) vals[k][e] = round_to<T>(vals[k][e] + d[e]);
+                if (!rows) store16(x + src + (size_t)i * V, vals[k]);
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss += vals[k][e] * vals[k][e];
+        }
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float o[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) o[e] = round_to<T>(vals[k][e] * rstd) * to_f32(w[(size_t)i * V + e]);
+            store16(y + (size_t)r * hidden + (size_t)i * V, o);
+        }
+    }
+}
+
 MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
                              int hidden, float eps, int dtype, int w_dtype, cudaStream_t stream) {
     if (num_rows == 0) return 0;
@@ -138,7 +182,13 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
     const int vw = dtype == MI_BF16 ? 8 : 4;
     const bool vec = hidden % vw == 0 && hidden / vw <= NT * (dtype == MI_BF16 ? 4 : 8) &&
                      ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    const int nvec = hidden / vw;
+    const bool by_warp = vec && num_rows >= 64 && nvec <= 32 * 16;
 #define LAUNCH(T, WT) do { \
+        if (by_warp && nvec <= 32 * 4) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 4>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 8) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 8>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 12) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 12>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 16>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
         if (vec) return (int)launch_pdl(add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
         return (int)launch_pdl(add_rmsnorm_kernel<T, WT, NT>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
     } while (0)

@@ -64,6 +64,42 @@ def test_add_rmsnorm(ops, dtype, hidden, w32):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [64, 2560, 4096, 5120, 1001])
+def test_add_rmsnorm_many_rows(ops, dtype, hidden):
+    """Row counts at which the one-warp-per-row kernel is used."""
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(203, hidden, generator=g) * 2).to(dtype).to(DEV)
+    d = torch.randn(203, hidden, generator=g).to(dtype).to(DEV)
+    w = (torch.rand(hidden, generator=g) + 0.5).to(dtype).to(DEV)
+    ref = TorchRefOps()
+    x1, x2 = x.clone(), x.clone()
+    close(ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6), dtype)
+    assert torch.equal(x1, x2)
+    rows = torch.arange(0, 203, 2, dtype=torch.int32, device=DEV)
+    close(ops.add_rmsnorm(x.clone(), None, w, 1e-6, rows), ref.add_rmsnorm(x.clone(), None, w, 1e-6, rows), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,D,page", [(4, 2, 16, 8), (32, 8, 128, 16), (5, 1, 48, 16)])
+def test_qk_norm_rope_cache_long_prompt(ops, dtype, H, KV, D, page):
+    """Token counts at which the one-block-per-token kernel is used."""
+    g = torch.Generator().manual_seed(12)
+    meta = make_meta(page, [(3, 300), (100, 41)], 64, seed=5)
+    qkv = torch.randn(meta.num_tokens, (H + 2 * KV) * D, generator=g).to(dtype).to(DEV)
+    qw = (torch.rand(D, generator=g) + 0.5).to(dtype).to(DEV)
+    kw = (torch.rand(D, generator=g) + 0.5).to(dtype).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(DEV)
+    shape = (65, KV, page, D)
+    k1, v1 = torch.zeros(shape, dtype=dtype, device=DEV), torch.zeros(shape, dtype=dtype, device=DEV)
+    k2, v2 = k1.clone(), v1.clone()
+    q1 = ops.qk_norm_rope_cache(qkv.clone(), H, KV, D, qw, kw, 1e-6, inv_freq, meta, k1, v1)
+    q2 = TorchRefOps().qk_norm_rope_cache(qkv.clone(), H, KV, D, qw, kw, 1e-6, inv_freq, meta, k2, v2)
+    close(q1, q2, dtype)
+    close(k1, k2, dtype)
+    assert torch.equal(v1, v2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(ops, dtype):
     g = torch.Generator().manual_seed(2)
     gu = (torch.randn(13, 2 * 223, generator=g) * 4).to(dtype).to(DEV)
