@@ -135,9 +135,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     const int cw = warp - 1, g = lane >> 2, c = lane & 3;
     const int ctid = threadIdx.x - 32;
     pdl_wait();                                            // before the first write to out / workspace
-    float acc[NT][4];
+    // four independent accumulation chains per token group (one per 16 k of a stage), added in a fixed order at the
+    // end of a share: a chain of dependent mma.sync would leave the warp waiting on each one's latency
+    float chain[NT][4][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { chain[nt][q][0] = chain[nt][q][1] = chain[nt][q][2] = chain[nt][q][3] = 0.f; }
     const int r_lo = cw * 16 + g, r_hi = r_lo + 8;
     int seg_start_kc = (int)(u0 % NKC);
 
@@ -147,17 +151,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         if (!mbar_wait(full0 + 8 * s, (i / NS) & 1)) { atomicExch(error_word, 2); return; }
         const unsigned char* st = base + s * STAGE;
         const unsigned char* xs = st + STAGE_BYTES;
+        // chunk 2c + win: the eight lanes of a quarter-warp then read eight different 16-byte columns of the
+        // swizzled rows (no bank conflicts); which k a lane takes does not matter as long as A and B agree
 #pragma unroll
         for (int win = 0; win < 2; ++win) {
-            const int ch = win * 4 + c;
+            const int ch = 2 * c + win;
             const uint4 a_lo = *reinterpret_cast<const uint4*>(st + r_lo * 128 + ((ch ^ (r_lo & 7)) << 4));
             const uint4 a_hi = *reinterpret_cast<const uint4*>(st + r_hi * 128 + ((ch ^ (r_hi & 7)) << 4));
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int t = nt * 8 + g;                  // rows beyond M were filled with zeros by the copy
                 const uint4 b = *reinterpret_cast<const uint4*>(xs + t * 128 + ((ch ^ (t & 7)) << 4));
-                mma16816(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-                mma16816(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+                mma16816(chain[nt][2 * win], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+                mma16816(chain[nt][2 * win + 1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
             }
         }
         __syncwarp();
@@ -165,6 +171,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 
         if (kc != NKC - 1 && u != u1 - 1) continue;
         // ---------------- this block's share of row tile rt ends here
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int f = 0; f < 4; ++f) acc[nt][f] = (chain[nt][0][f] + chain[nt][1][f]) + (chain[nt][2][f] + chain[nt][3][f]);
         const bool whole = seg_start_kc == 0 && kc == NKC - 1;
         if (whole) {
 #pragma unroll
@@ -218,7 +229,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             consumer_sync();
         }
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { chain[nt][q][0] = chain[nt][q][1] = chain[nt][q][2] = chain[nt][q][3] = 0.f; }
         seg_start_kc = 0;
     }
 }

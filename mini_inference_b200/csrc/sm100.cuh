@@ -34,6 +34,12 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {      // answers at once
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // false when the phase did not complete within the limit (the caller records an error and moves on)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
@@ -61,6 +67,10 @@ __device__ __forceinline__ float fast_exp2(float x) {      // ex2.approx: 2 ulp,
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                  :: "r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// asks for the box to be brought into L2; nothing is written and nothing signals completion
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" :: "l"((uint64_t)map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];\n" :: "l"((uint64_t)map) : "memory");

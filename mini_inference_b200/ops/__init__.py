@@ -77,6 +77,11 @@ class CudaOps:
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
+        # few rows: out-projection, norm and feed-forward of a block as one persistent kernel (csrc/decode_chain.cu).
+        # Measured at Qwen3-4B sizes, 8 rows: 52 us against ~50 us for the separate kernels (its three products run
+        # at 5.9 TB/s, but five grid-wide barriers and the passes between them cost ~20 us), so it is off unless asked for.
+        self.decode_chain_on = os.environ.get("MI_DECODE_CHAIN", "0") == "1"
+        self._chain_plans, self._chain_state = {}, None
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -270,12 +275,49 @@ class CudaOps:
         self.launches += 1
         return out
 
+    def decode_chain(self, attn, w_out, x, norm_w, eps, w_gate_up, w_down):
+        """x += attn @ w_out.T; returns (silu(g) * u) @ w_down.T with [g | u] = rmsnorm(x) @ w_gate_up.T, all in
+        one launch, or None when these sizes or dtypes are not taken (the caller then runs the separate kernels)."""
+        M, q_dim = attn.shape
+        hidden, inter = x.shape[1], w_down.shape[1]
+        tensors = (attn, w_out, x, norm_w, w_gate_up, w_down)
+        if (not self.decode_chain_on or M > 16 or any(t.dtype != torch.bfloat16 for t in tensors)
+                or not (x.is_contiguous() and w_out.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous())
+                or attn.stride(1) != 1 or attn.stride(0) % 8):
+            return None
+        key = (8 if M <= 8 else 16, hidden, q_dim, inter)
+        plan = self._chain_plans.get(key)
+        if plan is None:
+            ws = _c.c_longlong()
+            rc = self.lib.mi_decode_chain_plan(key[0], hidden, q_dim, inter, _c.byref(ws))
+            plan = self._chain_plans[key] = False if rc else ws.value
+        if not plan:
+            return None
+        ws_floats = plan
+        if self._chain_state is None:        # allocated once: captured graphs keep this address
+            self._chain_state = torch.zeros(1, dtype=torch.int64, device=x.device)
+        if self._stream_error is None:
+            self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
+            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
+        workspace = torch.empty(ws_floats, dtype=torch.float32, device=x.device)
+        gate_up = torch.empty((M, 2 * inter), dtype=torch.bfloat16, device=x.device)
+        act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+        out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
+        rc = self.lib.mi_decode_chain(_p(attn), attn.stride(0), _p(w_out), _p(x), x.stride(0), _p(norm_w), _c.c_float(eps),
+                                      _p(w_gate_up), _p(gate_up), _p(w_down), _p(act), _p(out), M, hidden, q_dim, inter,
+                                      _p(workspace), _p(self._chain_state), _p(self._stream_error), self._stream())
+        if rc == -2:
+            return None
+        _check(rc, "decode_chain")
+        self.launches += 1
+        return out
+
     def check_errors(self):
         """Raises if a bounded wait inside a kernel ran out (synchronises the device)."""
         if self._stream_error is not None and int(self._stream_error.item()) != 0:
             code = int(self._stream_error.item())
             self._stream_error.zero_()
-            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention)")
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention, 41-45 decode_chain)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):

@@ -44,6 +44,11 @@ class GQAAttention(Part):
         self.q_norm, self.k_norm = tensors.get("q_norm"), tensors.get("k_norm")
 
     def forward(self, h, ctx, cache, position, owns_cache=True):
+        o, w = self.forward_open(h, ctx, cache, position, owns_cache)
+        return ctx.ops.linear(o, w)
+
+    def forward_open(self, h, ctx, cache, position, owns_cache=True):
+        """Everything but the output projection: (attention rows [T, H*D], o_proj weight)."""
         ops = ctx.ops
         meta = ctx.batch.groups[cache.group]
         qkv = ops.linear(h, self.qkv)
@@ -52,4 +57,4 @@ class GQAAttention(Part):
             position.rotary_inv_freq(), meta, cache.k if owns_cache else None,
             cache.v if owns_cache else None)
         o = ops.paged_attention(q, cache.k, cache.v, meta, self.H, self.KV, self.D, self.scale, self.window)
-        return ops.linear(o, self.o)
+        return o, self.o

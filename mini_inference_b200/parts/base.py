@@ -21,6 +21,13 @@ Interfaces
   Block        __init__(spec, mixer, feed_forward, norm1, norm2, position)
                forward(x, delta, ctx, cache, owns_cache) -> (x, delta)
                    x is the residual stream, delta an addition not yet applied to it
+
+Optional fast-path protocol (a block may use it when all three parts offer it; none has to):
+  Mixer        forward_open(h, ctx, cache, position, owns_cache) -> (rows, out_weight)
+                   forward() without its last product: forward == linear(rows, out_weight)
+  Norm         rms_params() -> (weight, eps)   when forward is the plain RMS norm
+  FeedForward  gated_weights() -> (gate_up [2I, hidden], down [hidden, I])
+                   when forward == linear(silu(g) * u, down) with [g | u] = linear(h, gate_up)
 """
 from __future__ import annotations
 

@@ -1,7 +1,12 @@
 """Pre-norm residual arrangement (engine/core/model_runner.py:120-131):
 x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x)).  Each addition is carried as a
 pending delta into the next norm's kernel, which adds it to the residual stream (in float32,
-stored back in the stream's dtype) and normalises in one pass."""
+stored back in the stream's dtype) and normalises in one pass.
+
+When a step has few rows and the three parts offer the optional fast-path protocol (a mixer that
+can stop before its output projection, a plain RMS norm, a silu-gated feed-forward), everything
+after the mixer's core runs as one persistent kernel (ops.decode_chain); the kernel namespace
+decides whether it takes the sizes, and the separate kernels run otherwise."""
 from __future__ import annotations
 
 from .base import Part, register_block
@@ -13,8 +18,21 @@ class PreNormBlock(Part):
         super().__init__(spec)
         self.mixer, self.feed_forward, self.norm1, self.norm2, self.position = mixer, feed_forward, norm1, norm2, position
 
+        self.chain = (hasattr(mixer, "forward_open") and hasattr(norm2, "rms_params")
+                      and hasattr(feed_forward, "gated_weights"))
+
     def forward(self, x, delta, ctx, cache, owns_cache=True):
         h = self.norm1.forward(x, delta, ctx)
-        a = self.mixer.forward(h, ctx, cache, self.position, owns_cache)
+        chain = getattr(ctx.ops, "decode_chain", None) if self.chain else None
+        if chain is not None:
+            rows, w_out = self.mixer.forward_open(h, ctx, cache, self.position, owns_cache)
+            norm_w, eps = self.norm2.rms_params()
+            gate_up, down = self.feed_forward.gated_weights()
+            out = chain(rows, w_out, x, norm_w, eps, gate_up, down)
+            if out is not None:
+                return x, out
+            a = ctx.ops.linear(rows, w_out)
+        else:
+            a = self.mixer.forward(h, ctx, cache, self.position, owns_cache)
         h = self.norm2.forward(x, a, ctx)
         return x, self.feed_forward.forward(h, ctx)

@@ -28,3 +28,6 @@ class SwiGLU(Part):
     def forward(self, h, ctx):
         gu = ctx.ops.linear(h, self.gate_up)
         return ctx.ops.linear(ctx.ops.swiglu(gu), self.down)
+
+    def gated_weights(self):
+        return self.gate_up, self.down

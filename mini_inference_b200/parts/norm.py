@@ -22,3 +22,6 @@ class RMSNorm(Part):
 
     def forward(self, x, delta, ctx, rows=None):
         return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows)
+
+    def rms_params(self):
+        return self.weight, self.eps

@@ -346,3 +346,52 @@ def test_sampling_distribution(ops):
     freq = torch.bincount(got, minlength=7).float() / 4096
     probs = torch.softmax(logits[0].cpu() / 0.7, -1)
     assert (freq - probs).abs().max() < 0.03
+
+
+@pytest.fixture
+def chain_ops(ops):
+    """The kernel namespace with the optional fused block-tail kernel switched on (it is off by default)."""
+    ops.decode_chain_on = True
+    yield ops
+    ops.decode_chain_on = False
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("hidden,q_dim,inter", [(192, 128, 320), (2560, 4096, 9728), (640, 448, 1088), (1024, 2048, 3072)])
+def test_decode_chain(chain_ops, M, hidden, q_dim, inter):
+    """Out-projection + residual + norm + gated feed-forward as one persistent kernel against the separate kernels
+    (same rounding points: equal up to the order of float32 sums) and against float32 arithmetic."""
+    ops = chain_ops
+    g = torch.Generator().manual_seed(M * 1000 + hidden)
+    mk = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(torch.bfloat16).to(DEV)
+    attn, x = mk(M, q_dim), mk(M, hidden, scale=2.0)
+    w_o, w_gu, w_d = mk(hidden, q_dim, scale=q_dim ** -0.5), mk(2 * inter, hidden, scale=hidden ** -0.5), mk(hidden, inter, scale=inter ** -0.5)
+    norm_w = (torch.rand(hidden, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    eps = 1e-5
+    ref = TorchRefOps()
+    x_ref = x.clone()
+    h = ref.add_rmsnorm(x_ref, ref.linear(attn, w_o), norm_w, eps)
+    want = ref.linear(ref.swiglu(ref.linear(h, w_gu)), w_d)
+    for rep in range(3):                               # the kernel leaves its counters ready for the next call
+        x_own = x.clone()
+        got = ops.decode_chain(attn, w_o, x_own, norm_w, eps, w_gu, w_d)
+        assert got is not None, "sizes that the fused kernel must take"
+        ops.check_errors()
+        close(x_own, x_ref, torch.bfloat16)
+        close(got, want, torch.bfloat16)
+    # a strided view of the attention output (rows of a wider buffer) gives the same result
+    wide = torch.zeros(M, q_dim + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :q_dim] = attn
+    x2 = x.clone()
+    got2 = ops.decode_chain(wide[:, :q_dim], w_o, x2, norm_w, eps, w_gu, w_d)
+    ops.check_errors()
+    assert torch.equal(got2, got) and torch.equal(x2, x_own)
+
+
+def test_decode_chain_refuses(chain_ops):
+    ops = chain_ops
+    mk = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=DEV)
+    # 17 rows, a width that is no multiple of 64, float32 rows: the caller is told to use the separate kernels
+    assert ops.decode_chain(mk(17, 128), mk(192, 128), mk(17, 192), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
+    assert ops.decode_chain(mk(4, 128), mk(200, 128), mk(4, 200), mk(200), 1e-5, mk(640, 200), mk(200, 320)) is None
+    assert ops.decode_chain(mk(4, 128), mk(192, 128), mk(4, 192).float(), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
