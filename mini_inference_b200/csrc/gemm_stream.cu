@@ -194,12 +194,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             const long long first_unit = (long long)rt * NKC;
             const int first = owner_of(first_unit, U, G), last = owner_of(first_unit + NKC - 1, U, G);
             const int slot = (int)blockIdx.x - first, contrib = last - first + 1;
-            float* mine = workspace + ((size_t)rt * max_contrib + slot) * TR * TOK;
+            float* mine = workspace + ((size_t)rt * max_contrib + slot) * TR * TOK;     // [token][row]
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int t = nt * 8 + 2 * c;
-                mine[r_lo * TOK + t] = acc[nt][0]; mine[r_lo * TOK + t + 1] = acc[nt][1];
-                mine[r_hi * TOK + t] = acc[nt][2]; mine[r_hi * TOK + t + 1] = acc[nt][3];
+                mine[t * TR + r_lo] = acc[nt][0]; mine[(t + 1) * TR + r_lo] = acc[nt][1];
+                mine[t * TR + r_hi] = acc[nt][2]; mine[(t + 1) * TR + r_hi] = acc[nt][3];
             }
             __threadfence();
             consumer_sync();
@@ -207,22 +207,28 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             consumer_sync();
             if (last_flag) {                                   // every other share of this tile is in the workspace
                 __threadfence();
+                // four rows of one token per thread, every share's piece requested before the first is added (in share
+                // order): the block that arrives last is on the kernel's critical path, so this is one round trip to L2
                 const float* tile_ws = workspace + (size_t)rt * max_contrib * TR * TOK;
-                for (int idx = ctid; idx < TR * TOK; idx += CONSUMERS * 32) {
-                    const int t = idx / TR, r = idx % TR;
-                    if (t < M && rt * TR + r < N) {
-                        const float* src = tile_ws + (size_t)r * TOK + t;
-                        float sum = 0.f;
-                        for (int k0 = 0; k0 < contrib; k0 += 8) {      // 8 independent loads in flight, added in share order
-                            float v[8];
+                for (int idx = ctid; idx < TR * TOK / 4; idx += CONSUMERS * 32) {
+                    const int t = idx / (TR / 4), r = (idx % (TR / 4)) * 4;
+                    if (t >= M || rt * TR + r >= N) continue;
+                    const float* src = tile_ws + (size_t)t * TR + r;
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int k0 = 0; k0 < contrib; k0 += 12) {
+                        float4 v[12];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                v[j] = k0 + j < contrib ? __ldcg(src + (size_t)(k0 + j) * TR * TOK) : 0.f;
+                        for (int j = 0; j < 12; ++j)
+                            v[j] = k0 + j < contrib ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(k0 + j) * TR * TOK))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) sum += v[j];
-                        }
-                        out[(size_t)t * ldo + rt * TR + r] = cvt_out<OutT>(sum);
+                        for (int j = 0; j < 12; ++j) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
                     }
+                    OutT* dst = out + (size_t)t * ldo + rt * TR + r;
+                    const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (rt * TR + r + e < N) dst[e] = cvt_out<OutT>(vals[e]);
                 }
                 if (ctid == 0) counters[rt] = 0;               // ready for the next call
             }
