@@ -187,7 +187,8 @@ def prefill(llm, torch, tokens, vocab, warmup=3, reps=3):
 
 def profile(args, cfg, torch, LLM):
     """A small, bounded run for a profiler: no prefill before the decode steps (the cache holds
-    zeros at the benchmark's context length), one graph bucket, few launches."""
+    zeros at the benchmark's context length), one graph bucket, few launches.  The timed steps sit
+    between cudaProfilerStart and cudaProfilerStop (ncu --profile-from-start off captures only them)."""
     from mini_inference_b200.engine.batch import StepEntry
     from mini_inference_b200.engine.graphs import DecodeGraphs
     vocab = cfg["vocab_size"]
@@ -195,10 +196,22 @@ def profile(args, cfg, torch, LLM):
               kv_cache_tokens=args.batch * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=args.batch,
               max_model_len=args.ctx, max_batched_tokens=4096, cuda_graphs=False)
     if args.profile == "prefill":
-        ms = prefill(llm, torch, 2048, vocab, warmup=1, reps=args.steps)
+        prefill(llm, torch, 2048, vocab, warmup=0, reps=1)
+        torch.cuda.profiler.start()
+        ms = prefill(llm, torch, 2048, vocab, warmup=0, reps=args.steps)
+        torch.cuda.profiler.stop()
         print(f"prefill 2048 tokens: {ms:.3f} ms")
         return 0
-    llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32})
+    # which kernel runs each product is timed at start-up; under a profiler those timings are distorted, so a
+    # plain run can save its table (--choices FILE) and the profiled run of the same command reads it back
+    if args.choices and os.path.isfile(args.choices):
+        with open(args.choices) as f:
+            llm.ops._linear_choice = {tuple(int(v) for v in k.split(",")): c for k, c in json.load(f).items()}
+    else:
+        llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32})
+        if args.choices:
+            with open(args.choices, "w") as f:
+                json.dump({",".join(str(v) for v in k): c for k, c in llm.ops._linear_choice.items()}, f)
     llm.graphs = DecodeGraphs(llm.runner, args.batch, buckets=[args.batch])
     llm.graphs.capture()
     seqs = []
@@ -211,6 +224,7 @@ def profile(args, cfg, torch, LLM):
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for i in range(args.warmup + args.steps):
         if i == args.warmup:
+            torch.cuda.profiler.start()
             start.record()
         for s in seqs:
             llm.cache.ensure(s, s.num_tokens + 1)
@@ -221,6 +235,7 @@ def profile(args, cfg, torch, LLM):
             llm.cache.commit(s, s.num_tokens + 1)
     stop.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     print(f"decode b{B} ctx{args.ctx}: {start.elapsed_time(stop) / args.steps:.3f} ms/step, "
           f"{G.launches[B]} own kernels per step")
     return 0
@@ -237,6 +252,7 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--choices", default=None, help="--profile decode: file to keep the start-up choice of GEMM kernels in")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run only a few decode steps (cache filled without a prefill) or one prefill, for ncu")
     args = ap.parse_args()
