@@ -89,6 +89,32 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const float*
     }
 }
 
+// the same on 16 bytes already in registers
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& raw, float* out) {
+    if constexpr (sizeof(T) == 4) {
+        out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+        out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+    } else {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { out[2 * i] = __uint_as_float(w[i] << 16); out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+}
+template <typename T> __device__ __forceinline__ uint4 pack16(const float* v) {
+    uint4 raw;
+    if constexpr (sizeof(T) == 4) {
+        raw = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    } else {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    return raw;
+}
+
 template <typename T, typename WT, int NT, int VPT>
 __global__ void __launch_bounds__(NT)
 add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
@@ -131,45 +157,60 @@ add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT*
     }
 }
 
-// Many rows: one WARP per row (shuffles only, no block barrier), 8 rows per block.
+// Many rows: one WARP per row (shuffles only, no block barrier), 4 rows per block.  Every 16-byte piece of the row and
+// of the addition is requested before the first is used: a store to x between two loads of x would make the compiler
+// keep them in order, one round trip to memory each.  The summed row stays packed in registers for the second pass.
 template <typename T, typename WT, int VPT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 add_rmsnorm_warp_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
                         const int* __restrict__ rows, int num_rows, int hidden, float eps) {
     constexpr int V = Vec16<T>::N;
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (r >= num_rows) return;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const int nvec = hidden / V;
-    float vals[VPT][V];
+    uint4 xr[VPT], dr[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = lane + k * 32;
+        xr[k] = i < nvec ? *reinterpret_cast<const uint4*>(x + src + (size_t)i * V) : make_uint4(0, 0, 0, 0);
+    }
+    if (delta) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int i = lane + k * 32;
+            dr[k] = i < nvec ? *reinterpret_cast<const uint4*>(delta + src + (size_t)i * V) : make_uint4(0, 0, 0, 0);
+        }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int i = lane + k * 32;
-        if (i < nvec) {
-            load16(x + src + (size_t)i * V, vals[k]);
-            if (delta) {
-                float d[V];
-                load16(delta + src + (size_t)i * V, d);
+        float v[V];
+        unpack16<T>(xr[k], v);
+        if (delta) {
+            float d[V];
+            unpack16<T>(dr[k], d);
 #pragma unroll
-                for (int e = 0; e < V; ++e) vals[k][e] = round_to<T>(vals[k][e] + d[e]);
-                if (!rows) store16(x + src + (size_t)i * V, vals[k]);
-            }
-#pragma unroll
-            for (int e = 0; e < V; ++e) ss += vals[k][e] * vals[k][e];
+            for (int e = 0; e < V; ++e) v[e] = round_to<T>(v[e] + d[e]);
+            xr[k] = pack16<T>(v);
+            if (!rows && i < nvec) *reinterpret_cast<uint4*>(x + src + (size_t)i * V) = xr[k];
         }
+#pragma unroll
+        for (int e = 0; e < V; ++e) ss += v[e] * v[e];
     }
     const float rstd = rsqrtf(warp_sum(ss) / (float)hidden + eps);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int i = lane + k * 32;
         if (i < nvec) {
-            float o[V];
+            float v[V], o[V];
+            unpack16<T>(xr[k], v);
 #pragma unroll
-            for (int e = 0; e < V; ++e) o[e] = round_to<T>(vals[k][e] * rstd) * to_f32(w[(size_t)i * V + e]);
+            for (int e = 0; e < V; ++e) o[e] = round_to<T>(v[e] * rstd) * to_f32(w[(size_t)i * V + e]);
             store16(y + (size_t)r * hidden + (size_t)i * V, o);
         }
     }
@@ -185,10 +226,10 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
     const int nvec = hidden / vw;
     const bool by_warp = vec && num_rows >= 64 && nvec <= 32 * 16;
 #define LAUNCH(T, WT) do { \
-        if (by_warp && nvec <= 32 * 4) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 4>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp && nvec <= 32 * 8) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 8>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp && nvec <= 32 * 12) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 12>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 16>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 4) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 4>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 8) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 8>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 12) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 12>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
+        if (by_warp) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 16>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
         if (vec) return (int)launch_pdl(add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
         return (int)launch_pdl(add_rmsnorm_kernel<T, WT, NT>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
     } while (0)
