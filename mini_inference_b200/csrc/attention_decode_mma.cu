@@ -21,6 +21,9 @@
 // Needs page_size % 16 == 0 (a 16-key block never straddles a page) and G <= 16.
 #include "sm100.cuh"
 #include <math.h>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 using namespace mi;
 
@@ -46,13 +49,16 @@ constexpr int DEC_WARPS = 4;
 constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per warp
 
 // BULK = false: K/V go from the pages straight into registers (one block ahead).
-// BULK = true:  each warp keeps a ring of DEC_STAGES (K tile, V tile) pairs in shared memory, filled by
-//               cp.async.bulk (one 16-key x D tile of a page and kv head is contiguous in the cache), signalled
-//               by per-warp mbarriers; fragments are then read from shared memory.  More bytes in flight per SM
-//               at no register cost.
+// BULK = true:  each warp keeps a ring of DEC_STAGES (K tile, V tile) pairs in shared memory, filled by TMA tile
+//               loads ([16 keys x 64] boxes of the cache seen as a [rows, D] matrix, 128-byte swizzle), signalled
+//               by per-warp mbarriers; fragments are then read from shared memory without bank conflicts (the
+//               swizzle spreads the 8 keys of a quarter-warp over the banks; the score product takes its 16-byte
+//               pieces in the order 2c + (j & 1) so that neighbouring lanes also differ in the column).  More bytes
+//               in flight per SM at no register cost.
 template <int D, bool BULK>
 __global__ void __launch_bounds__(DEC_WARPS * 32, BULK ? 2 : 3)
-attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                       const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
@@ -61,7 +67,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
-    extern __shared__ float smem[];     // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
+    extern __shared__ float smem_raw[];  // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
+    float* smem = smem_raw;
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -84,6 +91,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     constexpr int RING_BYTES = BULK ? DEC_WARPS * DEC_STAGES * 2 * TILE : 0;
     constexpr int FRONT = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;   // the merge scratch re-uses the ring
     unsigned char* smem_bytes = reinterpret_cast<unsigned char*>(smem);
+    if (BULK) {                                            // swizzle atoms are 1 KB
+        smem_bytes = (unsigned char*)(((uintptr_t)smem_bytes + 1023) & ~(uintptr_t)1023);
+        smem = reinterpret_cast<float*>(smem_bytes);
+    }
     uint4* q_frag = reinterpret_cast<uint4*>(smem_bytes + FRONT);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bytes + FRONT + (D / 16) * 32 * 16);
     unsigned char* ring = smem_bytes + warp * (DEC_STAGES * 2 * TILE);
@@ -97,8 +108,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
 #pragma unroll
         for (int j = 0; j < KS / 2; ++j) {
             uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
-            if (g < G) r0 = *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + 32 * j + 8 * c);
-            if (g + 8 < G) r1 = *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + 32 * j + 8 * c);
+            const int d = BULK ? 64 * (j >> 1) + 16 * c + 8 * (j & 1) : 32 * j + 8 * c;   // the keys' pieces use the same order
+            if (g < G) r0 = *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + d);
+            if (g + 8 < G) r1 = *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + d);
             q_frag[(2 * j) * 32 + lane] = make_uint4(r0.x, r1.x, r0.y, r1.y);
             q_frag[(2 * j + 1) * 32 + lane] = make_uint4(r0.z, r1.z, r0.w, r1.w);
         }
@@ -129,6 +141,25 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
                 vreg[i][hb] = *reinterpret_cast<const uint4*>(base + (size_t)key * D + 64 * hb + 8 * g);
         }
     };
+    // BULK: the same fragments from a swizzled tile in shared memory ([64-column half][16 keys][128 bytes])
+    auto frag_k_sw = [&](const unsigned char* tile) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int j = 0; j < KS / 2; ++j) {
+                const int key = nt * 8 + g, piece = 2 * c + (j & 1);
+                kreg[nt][j] = *reinterpret_cast<const uint4*>(tile + (j >> 1) * 2048 + key * 128 + ((piece ^ (key & 7)) << 4));
+            }
+    };
+    auto frag_v_sw = [&](const unsigned char* tile) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = 2 * c + (i & 1) + 8 * (i >> 1);
+#pragma unroll
+            for (int hb = 0; hb < HALVES; ++hb)
+                vreg[i][hb] = *reinterpret_cast<const uint4*>(tile + hb * 2048 + key * 128 + ((g ^ (key & 7)) << 4));
+        }
+    };
     auto tile_of = [&](const __nv_bfloat16* cache, int blk) {
         const int page = table_row[(blk * 16) / ps];
         return cache + ((size_t)(page * KV + kvh) * ps + (blk * 16) % ps) * D;
@@ -138,13 +169,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
     // BULK: lane 0 asks for the K and V tiles of block `blk` into ring stage st
     auto issue = [&](int blk, int st) {
         if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the stage was just read with ordinary loads
             const uint32_t dst = sm100::smem_u32(ring + st * 2 * TILE), bar = bar0 + 8 * st;
+            const int page = table_row[(blk * 16) / ps];
+            const int row = (page * KV + kvh) * ps + (blk * 16) % ps;            // of the cache seen as [rows, D]
             sm100::mbar_expect_tx(bar, 2 * TILE);
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                         :: "r"(dst), "l"(tile_of(k_cache, blk)), "r"(TILE), "r"(bar) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                         :: "r"(dst + TILE), "l"(tile_of(v_cache, blk)), "r"(TILE), "r"(bar) : "memory");
+#pragma unroll
+            for (int hb = 0; hb < HALVES; ++hb) {
+                sm100::tma_load_2d(dst + hb * 2048, &kmap, hb * 64, row, bar);
+                sm100::tma_load_2d(dst + TILE + hb * 2048, &vmap, hb * 64, row, bar);
+            }
         }
     };
 
@@ -161,9 +195,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const 
         if (BULK) {
             const int st = nth % DEC_STAGES;
             if (!sm100::mbar_wait(bar0 + 8 * st, (nth / DEC_STAGES) & 1)) { if (lane == 0) atomicExch(error_word, 31); break; }
-            const __nv_bfloat16* tile = reinterpret_cast<const __nv_bfloat16*>(ring + st * 2 * TILE);
-            frag_k(tile);
-            frag_v(tile + 16 * D);
+            const unsigned char* tile = ring + st * 2 * TILE;
+            frag_k_sw(tile);
+            frag_v_sw(tile + TILE);
             __syncwarp();
             if (blk + DEC_STAGES * DEC_WARPS < b1) issue(blk + DEC_STAGES * DEC_WARPS, st);
         }
@@ -323,7 +357,7 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
-                                      int window, int* merge_counters, int* error_word, cudaStream_t stream);
+                                      int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream);
 
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
@@ -345,23 +379,50 @@ MI_EXPORT int mi_attn_decode_mma_fused(const void* q, int q_stride, const void* 
                                        int window, int* merge_counters, cudaStream_t stream) {
     return mi_attn_decode_mma_bulk(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode,
                                    seg_q_start, seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale,
-                                   window, merge_counters, nullptr, stream);
+                                   window, merge_counters, nullptr, 0, stream);
 }
 
-// error_word != null selects the variant that stages K/V through shared memory with cp.async.bulk and
-// per-warp mbarriers (bounded waits report through error_word); null keeps the register-streaming variant.
+// error_word != null selects the variant that stages K/V through shared memory with TMA tile loads and per-warp
+// mbarriers (bounded waits report through error_word; cache_pages = pages in k_cache / v_cache, for the tensor maps);
+// null keeps the register-streaming variant.
+namespace {
+std::mutex dec_mutex;
+std::map<std::tuple<const void*, long long, int>, CUtensorMap> dec_maps;
+int cache_map(const void* cache, long long rows, int D, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(dec_mutex);
+    auto key = std::make_tuple(cache, rows, D);
+    auto it = dec_maps.find(key);
+    if (it == dec_maps.end()) {
+        CUtensorMap m;
+        if (!sm100_host::make_map_bf16(&m, cache, (uint64_t)rows, (uint64_t)D, (uint64_t)D, 16, 64)) return -5;
+        it = dec_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+}  // namespace
+
 MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                       float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
-                                      int window, int* merge_counters, int* error_word, cudaStream_t stream) {
+                                      int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
     const bool bulk = error_word != nullptr;
+    CUtensorMap kmap = {}, vmap = {};
+    if (bulk) {
+        if (cache_pages < 1 || ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16)) return -2;
+        const long long rows = (long long)cache_pages * KV * ps;
+        int rc = cache_map(k_cache, rows, D, &kmap);
+        if (rc) return rc;
+        if ((rc = cache_map(v_cache, rows, D, &vmap))) return rc;
+    }
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
     const size_t ring_bytes = bulk ? (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 : 0;
-    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8;
+    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
+                        (bulk ? 1024 : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD, BB) do { \
         static bool configured = false; \
@@ -370,7 +431,7 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
-        return (int)launch_pdl(attn_decode_mma_kernel<DD, BB>, grid, dim3(DEC_WARPS * 32), smem, stream, \
+        return (int)launch_pdl(attn_decode_mma_kernel<DD, BB>, grid, dim3(DEC_WARPS * 32), smem, stream, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
             H, KV, ps, scale_log2, window, merge_counters, error_word); } while (0)

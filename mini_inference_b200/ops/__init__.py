@@ -67,9 +67,10 @@ class CudaOps:
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
         self._sample_slots = self._sample_arrivals = None
-        # decode attention can stage K/V through shared memory with cp.async.bulk; measured slower than streaming
-        # them into registers (37 vs 33 us at batch 8, context 4096), so it is off unless asked for
-        self.bulk_decode = os.environ.get("MI_BULK_DECODE", "0") == "1"
+        # decode attention stages K/V through shared memory with swizzled TMA tiles and per-warp mbarrier rings (31 vs
+        # 33 us at batch 8, 168 vs 202 us at batch 64, context 4096, against streaming them into registers);
+        # MI_BULK_DECODE=0 selects the register-streaming variant
+        self.bulk_decode = os.environ.get("MI_BULK_DECODE", "1") == "1"
         self.fused_merge = True              # the last split block to finish merges the splits (no merge launch)
         self._merge_counters = None
         self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
@@ -408,8 +409,8 @@ class CudaOps:
             _check(self.lib.mi_attn_decode_mma_bulk(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
-                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), _p(err_word), self._stream()),
-                "attn_decode_mma")
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), _p(err_word), k_cache.shape[0],
+                self._stream()), "attn_decode_mma")
             self.launches += 1
             if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,
