@@ -47,6 +47,8 @@ def main(argv=None) -> int:
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     p.add_argument("--cuda-graphs", default=None, choices=["on", "off"])
     p.add_argument("--chunked-prefill", default=None, choices=["on", "off"])
+    p.add_argument("--overlap-decode", default=None, choices=["on", "off"],
+                   help="with CUDA graphs: launch the next decode step before reading this one's tokens (default on)")
     p.add_argument("--max-batched-tokens", type=int, default=None, help="per-step token budget")
     p.add_argument("--max-num-seqs", type=int, default=None)
     p.add_argument("--max-model-len", type=int, default=None)
@@ -65,6 +67,7 @@ def main(argv=None) -> int:
     settings = dict(dtype=a.dtype, device=a.device, seed=a.sampling_seed)
     for key, val in (("cuda_graphs", None if a.cuda_graphs is None else a.cuda_graphs == "on"),
                      ("chunked_prefill", None if a.chunked_prefill is None else a.chunked_prefill == "on"),
+                     ("overlap_decode", None if a.overlap_decode is None else a.overlap_decode == "on"),
                      ("max_batched_tokens", a.max_batched_tokens), ("max_num_seqs", a.max_num_seqs),
                      ("max_model_len", a.max_model_len), ("kv_cache_tokens", a.kv_tokens), ("kv_cache_mb", a.kv_mb),
                      ("kv_block_size", a.page_size)):

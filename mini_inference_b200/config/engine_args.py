@@ -31,6 +31,9 @@ class EngineArgs:
     max_batched_tokens: int = field(default_factory=lambda: _env("MAX_BATCHED_TOKENS", int, 4096))  # config.py:111
     chunked_prefill: bool = field(default_factory=lambda: _env("CHUNKED_PREFILL", bool, False))     # config.py:117
     cuda_graphs: bool = field(default_factory=lambda: _env("CUDA_GRAPHS", bool, False))             # config.py:142
+    # with CUDA graphs: launch the next decode step (its tokens stay on the device) before the current one's tokens
+    # are read, so the host's bookkeeping overlaps the GPU; a request that stops on EOS has run one step in vain
+    overlap_decode: bool = field(default_factory=lambda: _env("OVERLAP_DECODE", bool, True))
     max_new_tokens: int = 100                                                                       # config.py:120
     do_sample: bool = False                                                                         # config.py:121
     temperature: float = 0.7                                                                        # config.py:122

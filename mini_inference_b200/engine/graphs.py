@@ -69,6 +69,7 @@ class DecodeGraphs:
         self.max_batch = max_batch
         self.batches, self.graphs, self.tokens_out, self.launches = {}, {}, {}, {}
         self.staging, self.events, self._turn = {}, {}, {}
+        self.out_host, self._out_turn = {}, {}
         self.replays = self.eager_steps = 0
         self.capture_s = 0.0
 
@@ -87,6 +88,8 @@ class DecodeGraphs:
             batch = _StaticBatch(B, self.cache, self.device, max_len, self.ops.prefill_tile)
             batch.view("seg_kv_len").fill_(1)                    # harmless rows: one key on the null page
             self.staging[B] = [torch.zeros(batch.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+            self.out_host[B] = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+            self._out_turn[B] = 0
             self.events[B] = [None] * self.RING
             self._turn[B] = 0
             side = torch.cuda.Stream(self.device)
@@ -169,29 +172,55 @@ class DecodeGraphs:
         self.replays += 1
         self.ops.launches += self.launches[B]
 
-    def run(self, chunks, sampler) -> Optional[List[int]]:
-        """The engine's decode step.  None when the step is not a pure decode step that fits a
-        bucket (engine/core/cuda_graphs.py:87)."""
+    def can_run(self, chunks) -> bool:
+        """A pure decode step that fits a bucket (engine/core/cuda_graphs.py:87)."""
+        return all(e - s == 1 and s > 0 for _, s, e in chunks) and self.bucket_for(len(chunks)) is not None
+
+    def launch(self, chunks, sampler, on_device_tokens: bool = False):
+        """Start one decode step and the copy of its sampled tokens to pinned host memory; returns a
+        handle for read().  on_device_tokens: the input tokens are the previous step's samples,
+        which are still on the device (same requests in the same rows); then nothing of the previous
+        step has to be known on the host, and each request's sample counter is one ahead of its
+        delivered tokens.  The cache's bookkeeping moves on at once: what the step wrote is ordered on
+        the stream before anything that could use those pages."""
         n = len(chunks)
-        if not all(e - s == 1 and s > 0 for _, s, e in chunks) or self.bucket_for(n) is None:
-            self.eager_steps += 1
-            return None
         B = self.bucket_for(n)
         reqs = [r for r, _, _ in chunks]
         seqs = [r.seq for r in reqs]
-        tokens = [r.all_ids[s] for r, s, _ in chunks]
+        tokens = None if on_device_tokens else [r.token_at(s) for r, s, _ in chunks]
         temps = [max(0.0, float(r.params.temperature)) for r in reqs]
         if any(t > 0 for t in temps):
             from ..sampling.sampler import request_seed
+            ahead = 1 if on_device_tokens else 0
             self.fill(B, seqs, tokens, temps, [request_seed(sampler.engine_seed, r) for r in reqs],
-                      [len(r.output_ids) for r in reqs])
+                      [len(r.output_ids) + ahead for r in reqs])
         else:
             self.fill(B, seqs, tokens)
+        if on_device_tokens:
+            self.feed_back(B)
         self.replay(B)
-        out = self.tokens_out[B][:n].tolist()                    # the step's one device->host sync
+        turn = self._out_turn[B]
+        self._out_turn[B] = (turn + 1) % self.RING
+        host = self.out_host[B][turn]
+        host[:n].copy_(self.tokens_out[B][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
         for (r, s, e), seq in zip(chunks, seqs):
             self.cache.commit(seq, e)
-        return out
+        return (host, ev, n)
+
+    def read(self, handle) -> List[int]:
+        """The step's sampled tokens (waits for that step only: its one device->host sync)."""
+        host, ev, n = handle
+        ev.synchronize()
+        return host[:n].tolist()
+
+    def run(self, chunks, sampler) -> Optional[List[int]]:
+        """The engine's decode step.  None when the step is not a pure decode step that fits a bucket."""
+        if not self.can_run(chunks):
+            self.eager_steps += 1
+            return None
+        return self.read(self.launch(chunks, sampler))
 
     def stats(self):
         return {"graph_replays": self.replays, "graph_eager_steps": self.eager_steps, "graph_buckets": len(self.buckets)}

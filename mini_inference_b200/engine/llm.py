@@ -17,7 +17,7 @@ from ..config.engine_args import EngineArgs
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
 from .factory import DTYPES, load_model
-from .request import FINISHED, Request, SamplingParams
+from .request import FINISHED, RUNNING, Request, SamplingParams
 from .runner import ModelRunner
 from .scheduler import Scheduler
 
@@ -73,6 +73,7 @@ class LLM:
             self.graphs = DecodeGraphs(self.runner, args.max_num_seqs)
             self.graphs.capture()
         self.last_error = None
+        self._ahead = None               # (chunks, handle) of a decode step launched but not yet delivered
         # step wall time split by kind (engine/custom_engine.py:69,140-142)
         self.step_time = {"decode": [0, 0.0], "other": [0, 0.0]}
 
@@ -108,32 +109,89 @@ class LLM:
         self.scheduler.add(req)
         return req
 
-    def has_work(self) -> bool:
-        return self.scheduler.has_work()
-
     # ---------------------------------------------------------------- the loop body
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._ahead is not None
+
     def step(self) -> List[Request]:
         """Schedule, run, sample, deliver (engine/custom_engine.py:124-170).  Returns the
-        requests that finished in this step."""
-        now = time.perf_counter()
-        chunks = self.scheduler.schedule(now)
-        if not chunks:
-            return self._fail_unschedulable()
+        requests that finished in this step.
+
+        With CUDA graphs and overlap_decode a decode step is delivered one call after it was
+        launched: the call launches the step after it first (its input tokens are this step's
+        samples, still on the device), then waits for this step's tokens and does the bookkeeping
+        while the GPU already runs the next one."""
         start = time.perf_counter()
+        if self._ahead is not None:
+            chunks, handle = self._ahead
+            self._ahead = None
+        else:
+            chunks = self.scheduler.schedule(start)
+            if not chunks:
+                return self._fail_unschedulable()
+            handle = None
+            try:
+                if self.graphs is not None and self.graphs.can_run(chunks):
+                    handle = self.graphs.launch(chunks, self.sampler)
+                else:
+                    tokens = self._run(chunks)
+            except Exception as e:
+                return self._abort(e)
+            if handle is None:
+                self._time_step(chunks, start)
+                return self._deliver(chunks, tokens)
         try:
-            tokens = self._run(chunks)
-        except Exception as e:                                           # fail this batch, keep serving
-            self.last_error = f"{type(e).__name__}: {e}"
-            done = self.scheduler.abort_all()
-            for r in done:
-                self._finish(r, "error", error=self.last_error)
-            return done
+            nxt = self._launch_ahead(chunks)
+            tokens = self.graphs.read(handle)
+        except Exception as e:
+            return self._abort(e)
+        self._time_step(chunks, start)
+        done = self._deliver(chunks, tokens)
+        self._ahead = nxt
+        return done
+
+    def _launch_ahead(self, chunks):
+        """The decode step after the one in flight, for the same requests in the same rows, if it is
+        certain that all of them go on (nobody waits to be admitted, nobody reaches a length limit,
+        everybody gets a page); a request that turns out to have stopped on EOS is skipped at delivery."""
+        if not self.args.overlap_decode or self.scheduler.waiting:
+            return None
+        reqs = [r for r, _, _ in chunks]
+        if len(reqs) != len(self.scheduler.running) or any(a is not b for a, b in zip(reqs, self.scheduler.running)):
+            return None
+        for req, _, end in chunks:
+            if req.state != RUNNING or end != req.total_len:
+                return None                                              # a row of the step in flight is already dead
+            if len(req.output_ids) + 2 > req.params.max_new_tokens or end + 2 > self.max_model_len:
+                return None                                              # it finishes with the step in flight
+        for req, _, end in chunks:
+            if not self.cache.ensure(req.seq, end + 1):
+                return None                                              # out of pages: the scheduler decides who yields
+        ahead = [(req, end, end + 1) for req, _, end in chunks]
+        self.scheduler.count_decode_step(len(ahead))
+        return ahead, self.graphs.launch(ahead, self.sampler, on_device_tokens=True)
+
+    def _time_step(self, chunks, start):
         kind = "decode" if all(e - s == 1 and s > 0 for _, s, e in chunks) else "other"
         self.step_time[kind][0] += 1
         self.step_time[kind][1] += (time.perf_counter() - start) * 1e3
+
+    def _abort(self, e):
+        """Fail this batch, keep serving."""
+        self.last_error = f"{type(e).__name__}: {e}"
+        self._ahead = None
+        done = self.scheduler.abort_all()
+        for r in done:
+            self._finish(r, "error", error=self.last_error)
+        return done
+
+    def _deliver(self, chunks, tokens) -> List[Request]:
         now = time.perf_counter()
         done, row = [], 0
         for req, _, end in chunks:
+            if req.state != RUNNING:                                     # stopped while this step was already in flight
+                row += 1
+                continue
             req.num_computed = end
             if end < req.total_len:                                      # prompt not finished yet
                 continue

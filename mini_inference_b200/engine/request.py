@@ -41,6 +41,11 @@ class Request:
         """Prompt plus everything generated so far: what the model has to see."""
         return self.prompt_ids + self.output_ids
 
+    def token_at(self, i: int) -> int:
+        """all_ids[i] without building the list."""
+        n = len(self.prompt_ids)
+        return self.prompt_ids[i] if i < n else self.output_ids[i - n]
+
     @property
     def total_len(self):
         return len(self.prompt_ids) + len(self.output_ids)

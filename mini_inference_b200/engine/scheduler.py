@@ -144,6 +144,13 @@ class Scheduler:
             budget -= take
         return list(scheduled.values())
 
+    def count_decode_step(self, n: int) -> None:
+        """A decode step of the n running requests that the engine launched itself, ahead of time."""
+        self.steps += 1
+        self.decode_tokens += n
+        self.last_batch_size = self.last_step_tokens = n
+        self.max_step_tokens = max(self.max_step_tokens, n)
+
     # ---------------------------------------------------------------- leaving
     def finish(self, req: Request) -> None:
         self.running.remove(req)

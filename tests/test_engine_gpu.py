@@ -87,6 +87,43 @@ def test_generate_through_entry_point(tiny_dirs, dtype):
         assert all([x[:3] for x in o] == [x[:3] for x in want] for o in outs)
 
 
+def test_overlapped_decode_is_token_exact(tiny_dirs):
+    """Launching the next decode step before this one's tokens are read changes no token: greedy and sampled, requests
+    of different lengths (length stops at different steps), stops on EOS found mid-way (the step launched in vain is
+    dropped), and a request that arrives while a step is in flight."""
+    from mini_inference_b200 import LLM, SamplingParams
+    d, cfg, page = tiny_dirs["B"]
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=80 + n) for n in (2, 5, 9, 14)]
+    sps = [SamplingParams(max_new_tokens=m, temperature=t, seed=7 + i)
+           for i, (m, t) in enumerate([(17, 0.0), (9, 0.9), (25, 0.0), (13, 0.7)])]
+    runs = {}
+    for overlap in (False, True):
+        llm = LLM(d, dtype="float32", device=DEV, kv_block_size=page, kv_cache_tokens=1024, cuda_graphs=True,
+                  overlap_decode=overlap)
+        plain_out = llm.generate(prompts, sps)
+        # a token that some request produces in the middle of its output becomes the end-of-sequence token
+        eos = plain_out[2][10]
+        llm.eos_ids = {eos}
+        eos_out = llm.generate(prompts, sps)
+        # a late arrival: two requests run, the third is added after a few steps
+        llm.eos_ids = set()
+        reqs = [llm.add_request(p, sp) for p, sp in zip(prompts[:2], sps[:2])]
+        for _ in range(4):
+            llm.step()
+        reqs.append(llm.add_request(prompts[2], sps[2]))
+        while llm.has_work():
+            llm.step()
+        late_out = [list(r.output_ids) for r in reqs]
+        llm.cache.check_invariants()
+        assert llm.cache.free_pages() == llm.cache.num_pages
+        runs[overlap] = (plain_out, eos_out, late_out, llm.stats()["graph_replays"])
+    assert runs[True][:3] == runs[False][:3]
+    assert [len(o) for o in runs[True][0]] == [17, 9, 25, 13]
+    assert len(runs[True][1][2]) == 11 and runs[True][1][2] == runs[True][0][2][:11]      # stopped on the chosen token
+    assert runs[True][2] == [runs[True][0][0], runs[True][0][1], runs[True][0][2]]
+    assert runs[True][3] >= runs[False][3]                 # a few steps were launched in vain, none was lost
+
+
 def test_temperature_sampling_does_not_depend_on_company(tiny_dirs):
     from mini_inference_b200 import LLM, SamplingParams
     d, cfg, page = tiny_dirs["B"]
