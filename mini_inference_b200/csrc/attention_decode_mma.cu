@@ -70,7 +70,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     extern __shared__ float smem_raw[];  // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
     float* smem = smem_raw;
     pdl_trigger();
-    pdl_wait();
+    if (!BULK) pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, c = lane & 3;
     const int G = H / KV;
@@ -102,6 +102,31 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     if (BULK && lane == 0) {
         for (int st = 0; st < DEC_STAGES; ++st) sm100::mbar_init(bar0 + 8 * st, 1);
         sm100::mbar_init_fence();
+    }
+    // BULK: lane 0 asks for the K and V tiles of block `blk` into ring stage st
+    auto issue = [&](int blk, int st) {
+        if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the stage was just read with ordinary loads
+            const uint32_t dst = sm100::smem_u32(ring + st * 2 * TILE), bar = bar0 + 8 * st;
+            const int page = table_row[(blk * 16) / ps];
+            const int row = (page * KV + kvh) * ps + (blk * 16) % ps;            // of the cache seen as [rows, D]
+            sm100::mbar_expect_tx(bar, 2 * TILE);
+#pragma unroll
+            for (int hb = 0; hb < HALVES; ++hb) {
+                sm100::tma_load_2d(dst + hb * 2048, &kmap, hb * 64, row, bar);
+                sm100::tma_load_2d(dst + TILE + hb * 2048, &vmap, hb * 64, row, bar);
+            }
+        }
+    };
+
+    // BULK: the first stages are requested BEFORE waiting for the kernel ahead: it writes only the newest token's key
+    // and value (the last 16-key block of a request), and the block table and lengths were copied in before the step began.
+    int primed = 0;
+    if (BULK) {
+        __syncwarp();
+        for (; primed < DEC_STAGES && b0 + warp + primed * DEC_WARPS < min(b1, blk_hi - 1); ++primed)
+            issue(b0 + warp + primed * DEC_WARPS, primed);
+        pdl_wait();
     }
     if (warp == 0) {
         const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
@@ -166,30 +191,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     };
     auto load_k = [&](int blk) { frag_k(tile_of(k_cache, blk)); };
     auto load_v = [&](int blk) { frag_v(tile_of(v_cache, blk)); };
-    // BULK: lane 0 asks for the K and V tiles of block `blk` into ring stage st
-    auto issue = [&](int blk, int st) {
-        if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the stage was just read with ordinary loads
-            const uint32_t dst = sm100::smem_u32(ring + st * 2 * TILE), bar = bar0 + 8 * st;
-            const int page = table_row[(blk * 16) / ps];
-            const int row = (page * KV + kvh) * ps + (blk * 16) % ps;            // of the cache seen as [rows, D]
-            sm100::mbar_expect_tx(bar, 2 * TILE);
-#pragma unroll
-            for (int hb = 0; hb < HALVES; ++hb) {
-                sm100::tma_load_2d(dst + hb * 2048, &kmap, hb * 64, row, bar);
-                sm100::tma_load_2d(dst + TILE + hb * 2048, &vmap, hb * 64, row, bar);
-            }
-        }
-    };
-
     // Software pipeline.  Registers: the keys of block i+1 are requested right after the scores of block i,
     // the values of block i+1 right after block i's P*V.  BULK: DEC_STAGES blocks are in flight in the ring;
     // a block's fragments are copied to registers as soon as it lands and its stage is refilled at once.
     int blk = b0 + warp;
     int nth = 0;
     if (BULK) {
-        __syncwarp();
-        for (int st = 0; st < DEC_STAGES && blk + st * DEC_WARPS < b1; ++st) issue(blk + st * DEC_WARPS, st);
+        for (int st = primed; st < DEC_STAGES && blk + st * DEC_WARPS < b1; ++st) issue(blk + st * DEC_WARPS, st);
     } else if (blk < b1) { load_k(blk); load_v(blk); }
     for (; blk < b1; blk += DEC_WARPS, ++nth) {
         if (BULK) {
