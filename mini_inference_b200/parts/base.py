@@ -14,6 +14,7 @@ Interfaces
                    the rows to normalise (then x is left untouched)
   Position     rotary_inv_freq() -> float32 [D/2] tensor or None
                on_embedding(x, ctx) -> x       (absolute encodings add here; default: identity)
+                   may own tensors like any part (weight names under "position.<name>" of the first layer using it)
   FeedForward  forward(h, ctx) -> [T, hidden]
   Mixer        cache_need() -> KVCacheNeed | StateNeed | None
                forward(h, ctx, cache, position, owns_cache) -> [T, hidden]

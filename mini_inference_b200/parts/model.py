@@ -18,14 +18,19 @@ class DecoderModel:
         self.blocks = []
         self._owned: List[Tuple[str, WeightSpec, Part]] = []      # (checkpoint name, spec, owner)
         for layer in spec.layers:
+            names = dict(layer.weight_names)
             position = self._positions.get(layer.position)
-            if position is None:
+            if position is None:                       # one position part per distinct spec, shared by its layers;
                 position = self._positions[layer.position] = build_part("position", layer.position)
+                for ws in position.weight_specs():     # its tensors (if any) are named by the first layer that uses it
+                    key = f"position.{ws.name}"
+                    if key not in names:
+                        raise KeyError(f"the layer's weight_names has no entry for '{key}'")
+                    self._owned.append((names[key], ws, position))
             mixer = build_part("mixer", layer.mixer)
             ffn = build_part("feed_forward", layer.feed_forward)
             norm1, norm2 = build_part("norm", layer.norm), build_part("norm", layer.norm)
             self.blocks.append(build_part("block", PartSpec.of(layer.block), mixer, ffn, norm1, norm2, position))
-            names = dict(layer.weight_names)
             for role, part in (("mixer", mixer), ("feed_forward", ffn), ("norm1", norm1), ("norm2", norm2)):
                 for ws in part.weight_specs():
                     key = f"{role}.{ws.name}"
@@ -65,7 +70,8 @@ class DecoderModel:
                 seen.add(id(part))
                 part.load(per_part[id(part)], dtype, self.device)
         for position in self._positions.values():
-            position.load({}, dtype, self.device)
+            if id(position) not in seen:
+                position.load({}, dtype, self.device)
         self.embedding = tensors[self.spec.embedding_name]
         self.lm_head = self.embedding if self.spec.lm_head_name is None else tensors[self.spec.lm_head_name]
 

@@ -247,3 +247,140 @@ def test_attention_part(device, window, qk_norm):
                                    (hs @ w["v_proj"].T).view(n, KV, D), 0.3, window)
         assert torch.allclose(y[at:at + n], o.reshape(n, H * D) @ w["o_proj"].T, atol=2e-5)
         at += n
+
+
+# ---------------------------------------------------------------- a toy routed feed-forward and a toy learned position encoding
+from mini_inference_b200.parts import register_feed_forward, register_position  # noqa: E402
+
+
+@register_feed_forward("toy_routed")
+class ToyRouted(Part):
+    """Top-2 of E small experts: router logits and the softmax over the two chosen in float32, the experts' products
+    through the kernel namespace, an integer table that says where each router column's expert is stored."""
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.inter, self.E = spec.get("hidden_size"), spec.get("intermediate_size"), spec.get("experts")
+
+    def weight_specs(self):
+        return [WeightSpec("router", (self.E, self.hidden)), WeightSpec("w_in", (self.E * self.inter, self.hidden)),
+                WeightSpec("w_out", (self.E * self.hidden, self.inter)), WeightSpec("place", (self.E,), kind="table")]
+
+    def load(self, tensors, dtype, device):
+        self.router, self.place = tensors["router"], tensors["place"]
+        self.w_in = tensors["w_in"].view(self.E, self.inter, self.hidden)
+        self.w_out = tensors["w_out"].view(self.E, self.hidden, self.inter)
+
+    def forward(self, h, ctx):
+        logits = h.float() @ self.router.float().T
+        top, idx = logits.topk(2, dim=-1)
+        gate = torch.softmax(top, dim=-1)
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        for e in range(self.E):
+            rows, which = (idx == e).nonzero(as_tuple=True)
+            if rows.numel():
+                slot = int(self.place[e])
+                y = ctx.ops.linear(torch.relu(ctx.ops.linear(h[rows].contiguous(), self.w_in[slot])), self.w_out[slot])
+                out.index_add_(0, rows, y.float() * gate[rows, which, None])
+        return out.to(h.dtype)
+
+
+@register_position("toy_learned")
+class ToyLearnedPosition(Part):
+    """A learned absolute encoding: a row of its own table is added to each token's embedding; nothing is rotated."""
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size, self.max_pos = spec.get("hidden_size"), spec.get("max_position")
+
+    def weight_specs(self):
+        return [WeightSpec("table", (self.max_pos, self.size))]
+
+    def load(self, tensors, dtype, device):
+        self.table = tensors["table"]
+
+    def rotary_inv_freq(self):
+        return None
+
+    def on_embedding(self, x, ctx):
+        return (x.float() + self.table[ctx.batch.positions.long()].float()).to(x.dtype)
+
+
+def routed_spec(hidden=48, vocab=61, inter=40, experts=4):
+    norm = PartSpec.of("rmsnorm", size=hidden, eps=1e-5)
+    pos = PartSpec.of("toy_learned", hidden_size=hidden, max_position=128)
+    attn = PartSpec.of("gqa_attention", hidden_size=hidden, num_heads=3, num_kv_heads=1, head_dim=16, scale=0.25,
+                       qk_norm=False, window=None)
+    routed = PartSpec.of("toy_routed", hidden_size=hidden, intermediate_size=inter, experts=experts)
+    dense = PartSpec.of("swiglu", hidden_size=hidden, intermediate_size=inter)
+
+    def names(i, ffn_tensors):
+        p = f"l{i}."
+        d = {"norm1.weight": p + "n1", "norm2.weight": p + "n2", "position.table": "pos_table"}
+        d.update({f"mixer.{t}": p + t for t in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        d.update({f"feed_forward.{t}": p + t for t in ffn_tensors})
+        return tuple(sorted(d.items()))
+    layers = (LayerSpec("prenorm", attn, routed, norm, pos, names(0, ["router", "w_in", "w_out", "place"])),
+              LayerSpec("prenorm", attn, dense, norm, pos, names(1, ["gate_proj", "up_proj", "down_proj"])),
+              LayerSpec("prenorm", attn, routed, norm, pos, names(2, ["router", "w_in", "w_out", "place"])))
+    return ModelSpec(hidden_size=hidden, vocab_size=vocab, layers=layers, order=tuple(ExecStep(i) for i in range(3)),
+                     final_norm=norm, embedding_name="emb", final_norm_name="fn", lm_head_name=None, max_position=128)
+
+
+def routed_plain(w, ids, hidden=48, inter=40, experts=4):
+    n = len(ids)
+    x = plain.embed(ids, w["emb"]) + w["pos_table"][:n]
+    for i in range(3):
+        h = plain.rms_norm(x, w[f"l{i}.n1"], 1e-5)
+        q = (h @ w[f"l{i}.q_proj"].T).view(n, 3, 16)                 # nothing is rotated
+        k = (h @ w[f"l{i}.k_proj"].T).view(n, 1, 16)
+        v = (h @ w[f"l{i}.v_proj"].T).view(n, 1, 16)
+        x = x + plain.causal_attention(q, k, v, 0.25, None).reshape(n, hidden) @ w[f"l{i}.o_proj"].T
+        h = plain.rms_norm(x, w[f"l{i}.n2"], 1e-5)
+        if i == 1:
+            x = x + (torch.nn.functional.silu(h @ w[f"l{i}.gate_proj"].T) * (h @ w[f"l{i}.up_proj"].T)) @ w[f"l{i}.down_proj"].T
+            continue
+        logits = h @ w[f"l{i}.router"].T
+        top, idx = logits.topk(2, dim=-1)
+        gate = torch.softmax(top, dim=-1)
+        w_in = w[f"l{i}.w_in"].view(experts, inter, hidden)
+        w_out = w[f"l{i}.w_out"].view(experts, hidden, inter)
+        y = torch.zeros(n, hidden)
+        for t in range(n):
+            for j in range(2):
+                slot = int(w[f"l{i}.place"][idx[t, j]])
+                y[t] += gate[t, j] * (torch.relu(h[t] @ w_in[slot].T) @ w_out[slot].T)
+        x = x + y
+    return plain.rms_norm(x, w["fn"], 1e-5) @ w["emb"].T
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_toy_routed_feed_forward_and_learned_position(device):
+    """A feed-forward with routing (float32 router, an integer table among its tensors) and a position encoding with a
+    table of its own are registered here, chosen layer by layer beside a dense feed-forward, and stepped in portions."""
+    model = DecoderModel(routed_spec())
+    table = dict(model.weight_table())
+    assert table["pos_table"].shape == (128, 48) and table["l0.place"].kind == "table"
+    assert sum(name == "pos_table" for name, _ in model.weight_table()) == 1          # shared by the layers, loaded once
+    g = torch.Generator().manual_seed(11)
+    tensors = {}
+    for name, ws in model.weight_table():
+        if ws.kind == "table":
+            t = torch.randperm(ws.shape[0], generator=g).to(torch.int32)
+        elif ws.init == "norm":
+            t = torch.rand(ws.shape, generator=g) + 0.5
+        else:
+            t = torch.randn(ws.shape, generator=g) * 0.15
+        tensors[name] = t.to(device)
+    model.load(dict(tensors), torch.float32, device)
+    w = {k: (v.cpu() if v.dtype == torch.int32 else v.float().cpu()) for k, v in tensors.items()}
+    cache = CacheManager(model.cache_needs(), 4, 64, 4, 128, dtype=torch.float32, device=device)
+    runner = ModelRunner(model, cache, get_ops(device))
+    ids = torch.randint(0, 61, (37,), generator=g).tolist()
+    want = routed_plain(w, ids)
+    for cuts in ([37], [20] + [1] * 17, random_cuts(37, __import__("random").Random(9))):
+        seq, at, out = cache.admit("r"), 0, []
+        for n in cuts:
+            out.append(runner.step([StepEntry(seq, ids[at:at + n], range(n))]).float().cpu())
+            at += n
+        cache.free(seq)
+        assert rel_err(torch.cat(out), want) < 3e-5, cuts
+    cache.check_invariants()
