@@ -177,7 +177,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
             for (int f = 0; f < 4; ++f) acc[nt][f] = (chain[nt][0][f] + chain[nt][1][f]) + (chain[nt][2][f] + chain[nt][3][f]);
         const bool whole = seg_start_kc == 0 && kc == NKC - 1;
-        if (whole) {
+        if (whole && counters != nullptr) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int t = nt * 8 + 2 * c, n_lo = rt * TR + r_lo, n_hi = rt * TR + r_hi;
@@ -201,6 +201,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 mine[t * TR + r_lo] = acc[nt][0]; mine[(t + 1) * TR + r_lo] = acc[nt][1];
                 mine[t * TR + r_hi] = acc[nt][2]; mine[(t + 1) * TR + r_hi] = acc[nt][3];
             }
+            // deferred mode (no counters): the partial sums are the result; whoever reads them adds the shares of a
+            // tile in order (mi_deferred_add_rmsnorm / mi_deferred_reduce), and this kernel has no fix-up tail
+            if (counters != nullptr) {
             __threadfence();
             consumer_sync();
             if (ctid == 0) last_flag = atomicAdd(&counters[rt], 1) == contrib - 1;
@@ -231,6 +234,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                         if (rt * TR + r + e < N) dst[e] = cvt_out<OutT>(vals[e]);
                 }
                 if (ctid == 0) counters[rt] = 0;               // ready for the next call
+            }
             }
             consumer_sync();
         }
@@ -340,5 +344,23 @@ MI_EXPORT int mi_gemm_stream(const void* X, int ldx, const void* W, void* out, i
 #define GO(NT, OT) launch<NT, OT>(map, X, ldx, out, ldo, M, N, K, workspace, max_contrib, counters, error_word, grid, stream)
     if (out_dtype == MI_F32) return M <= 8 ? GO(1, float) : M <= 16 ? GO(2, float) : GO(4, float);
     return M <= 8 ? GO(1, __nv_bfloat16) : M <= 16 ? GO(2, __nv_bfloat16) : GO(4, __nv_bfloat16);
+#undef GO
+}
+
+// The same product left as partial sums: workspace [row_tiles][max_contrib][tokens_padded][128] float32 holds, for every
+// row tile, the shares of the blocks that worked on it (share s of tile t came from block first_owner(t) + s); nothing is
+// added up and nothing is written elsewhere.  mi_deferred_add_rmsnorm (the usual next kernel) or mi_deferred_reduce adds
+// the shares in order.  Same shapes and return codes as mi_gemm_stream.
+MI_EXPORT int mi_gemm_stream_deferred(const void* X, int ldx, const void* W, int M, int N, int K, float* workspace,
+                                      int* error_word, cudaStream_t stream) {
+    int grid, row_tiles, max_contrib;
+    int rc = mi_gemm_stream_plan(M, N, K, &grid, &row_tiles, &max_contrib);
+    if (rc) return rc;
+    if (ldx % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16) || (K * 2) % 16) return -2;
+    CUtensorMap map;
+    rc = get_weight_map(W, N, K, &map);
+    if (rc) return rc;
+#define GO(NT) launch<NT, __nv_bfloat16>(map, X, ldx, nullptr, 0, M, N, K, workspace, max_contrib, nullptr, error_word, grid, stream)
+    return M <= 8 ? GO(1) : M <= 16 ? GO(2) : GO(4);
 #undef GO
 }

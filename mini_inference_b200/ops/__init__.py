@@ -50,8 +50,23 @@ def _check(err, what):
         raise RuntimeError(f"{what}: CUDA error {err} at launch")
 
 
+class DeferredSum:
+    """A product [M, N] that the few-row GEMM left as partial sums (csrc/gemm_stream.cu, deferred mode).  Only
+    add_rmsnorm (as its `delta`) and CudaOps.materialize understand it; a part that gets one must pass it on untouched."""
+    __slots__ = ("ws", "M", "N", "K", "grid", "max_contrib", "tok", "device")
+
+    def __init__(self, ws, M, N, K, grid, max_contrib, tok):
+        self.ws, self.M, self.N, self.K, self.grid, self.max_contrib, self.tok = ws, M, N, K, grid, max_contrib, tok
+        self.device = ws.device
+
+    @property
+    def shape(self):
+        return (self.M, self.N)
+
+
 class CudaOps:
     prefill_tile = 64
+    deferred = True                          # linear(..., defer=True) may answer with a DeferredSum
     NUM_SMS = 148
 
     def __init__(self, device):
@@ -75,6 +90,9 @@ class CudaOps:
         self._merge_counters = None
         self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
         self._stream_plans, self._stream_counters, self._stream_error = {}, None, None
+        # a few-row product whose only reader is the next residual-add + norm is left as partial sums for that kernel
+        # to add up (no fix-up tail in the GEMM); MI_DEFER_SUMS=0 turns it off
+        self.defer_sums = os.environ.get("MI_DEFER_SUMS", "1") == "1"
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
@@ -99,6 +117,17 @@ class CudaOps:
 
     def add_rmsnorm(self, x, delta, weight, eps, rows=None):
         hidden = x.shape[-1]
+        if isinstance(delta, DeferredSum):
+            if rows is None and x.dtype == torch.bfloat16 and x.is_contiguous() and hidden % 4 == 0 and delta.shape == tuple(x.shape):
+                y = torch.empty_like(x)
+                rc = self.lib.mi_deferred_add_rmsnorm(_p(x), _p(delta.ws), _p(weight), _p(y), delta.M, delta.N, delta.K, delta.grid,
+                                                      delta.max_contrib, delta.tok, _c.c_float(eps), _code(weight.dtype), self._stream())
+                if rc == 0:
+                    self.launches += 1
+                    return y
+                if rc != -2:
+                    _check(rc, "deferred_add_rmsnorm")
+            delta = self.materialize(delta)
         assert x.is_contiguous() and (delta is None or delta.is_contiguous())
         n = x.shape[0] if rows is None else rows.shape[0]
         y = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
@@ -106,6 +135,16 @@ class CudaOps:
                                        _code(x.dtype), _code(weight.dtype), self._stream()), "add_rmsnorm")
         self.launches += 1
         return y
+
+    def materialize(self, value):
+        """The bfloat16 tensor behind a DeferredSum (anything else is returned as it is)."""
+        if not isinstance(value, DeferredSum):
+            return value
+        out = torch.empty((value.M, value.N), dtype=torch.bfloat16, device=value.device)
+        _check(self.lib.mi_deferred_reduce(_p(value.ws), _p(out), value.M, value.N, value.K, value.grid, value.max_contrib,
+                                           value.tok, self._stream()), "deferred_reduce")
+        self.launches += 1
+        return out
 
     def swiglu(self, gate_up):
         rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
@@ -116,8 +155,9 @@ class CudaOps:
         return out
 
     # ---------------------------------------------------------------- matrix products
-    def linear(self, x, w, out_dtype=None):
-        """x [M, K] (rows may be strided), w [N, K] -> [M, N]."""
+    def linear(self, x, w, out_dtype=None, defer=False):
+        """x [M, K] (rows may be strided), w [N, K] -> [M, N].  defer=True: the caller will use the result only as the
+        `delta` of add_rmsnorm (or pass it through materialize); the answer may then be a DeferredSum."""
         if x.dtype == torch.float32:
             M, K = x.shape
             N = w.shape[0]
@@ -137,7 +177,8 @@ class CudaOps:
             return self._library_linear(x, w, out_dtype)
         if (self.stream_gemm and choice in (None, "stream") and M <= 32 and w.shape[0] <= self.stream_max_cols and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
-            out = self._gemm_stream(x, w, out_dtype or x.dtype)
+            out = self._gemm_stream(x, w, out_dtype or x.dtype, defer=defer and self.defer_sums and choice == "stream"
+                                    and out_dtype in (None, torch.bfloat16) and w.shape[0] % 4 == 0)
             if out is not None:
                 return out
         if (self.skinny_gemm and (choice == "skinny" or (choice is None and M <= self.skinny_max_rows
@@ -234,7 +275,7 @@ class CudaOps:
         torch.cuda.synchronize(self.device)
         return start.elapsed_time(stop) * 1e3 / iters
 
-    def _gemm_stream(self, x, w, od):
+    def _gemm_stream(self, x, w, od, defer=False):
         """Persistent TMA weight-streaming product (csrc/gemm_stream.cu); None if the shape is not taken."""
         M, K = x.shape
         N = w.shape[0]
@@ -245,12 +286,20 @@ class CudaOps:
             plan = self._stream_plans[(M, N, K)] = None if rc else (g.value, rt.value, mc.value)
         if not plan:
             return None
-        _, row_tiles, max_contrib = plan
+        grid, row_tiles, max_contrib = plan
         if self._stream_counters is None or self._stream_counters.numel() < row_tiles:
             self._stream_counters = torch.zeros(max(row_tiles, 4096), dtype=torch.int32, device=x.device)
             self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
         tok = 8 if M <= 8 else 16 if M <= 16 else 32
         workspace = torch.empty(row_tiles * max_contrib * 128 * tok, dtype=torch.float32, device=x.device)
+        if defer:
+            rc = self.lib.mi_gemm_stream_deferred(_p(x), x.stride(0), _p(w), M, N, K, _p(workspace), _p(self._stream_error),
+                                                  self._stream())
+            if rc == 0:
+                self.launches += 1
+                return DeferredSum(workspace, M, N, K, grid, max_contrib, tok)
+            if rc != -2:
+                _check(rc, "gemm_stream_deferred")
         out = torch.empty((M, N), dtype=od, device=x.device)
         rc = self.lib.mi_gemm_stream(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), _p(workspace),
                                      _p(self._stream_counters), _p(self._stream_error), self._stream())

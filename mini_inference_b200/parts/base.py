@@ -23,10 +23,13 @@ Interfaces
                forward(x, delta, ctx, cache, owns_cache) -> (x, delta)
                    x is the residual stream, delta an addition not yet applied to it
 
-Optional fast-path protocol (a block may use it when all three parts offer it; none has to):
+Optional fast-path protocol (a block may use what its parts offer; none has to):
   Mixer        forward_open(h, ctx, cache, position, owns_cache) -> (rows, out_weight)
                    forward() without its last product: forward == linear(rows, out_weight)
-  Norm         rms_params() -> (weight, eps)   when forward is the plain RMS norm
+  FeedForward  forward_open(h, ctx) -> (rows, out_weight)      the same
+  Norm         accepts_deferred = True   when forward hands `delta` to ctx.ops.add_rmsnorm untouched: the block may then
+                   give it the result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
+               rms_params() -> (weight, eps)   when forward is the plain RMS norm
   FeedForward  gated_weights() -> (gate_up [2I, hidden], down [hidden, I])
                    when forward == linear(silu(g) * u, down) with [g | u] = linear(h, gate_up)
 """
@@ -74,6 +77,7 @@ class StepContext:
     """What a part sees of the step being run."""
     def __init__(self, ops, batch, dtype, device):
         self.ops, self.batch, self.dtype, self.device = ops, batch, dtype, device
+        self.defer_ok = False        # set by the model when every reader of a block's outputs accepts deferred sums
 
 
 class Part:

@@ -21,18 +21,27 @@ class PreNormBlock(Part):
         self.chain = (hasattr(mixer, "forward_open") and hasattr(norm2, "rms_params")
                       and hasattr(feed_forward, "gated_weights"))
 
+        self.open_mixer = hasattr(mixer, "forward_open")
+        self.open_ffn = hasattr(feed_forward, "forward_open")
+
     def forward(self, x, delta, ctx, cache, owns_cache=True):
+        ops = ctx.ops
         h = self.norm1.forward(x, delta, ctx)
-        chain = getattr(ctx.ops, "decode_chain", None) if self.chain else None
-        if chain is not None:
+        defer = ctx.defer_ok                   # the readers of `a` and of the returned delta are norms that accept it
+        if self.open_mixer:
             rows, w_out = self.mixer.forward_open(h, ctx, cache, self.position, owns_cache)
-            norm_w, eps = self.norm2.rms_params()
-            gate_up, down = self.feed_forward.gated_weights()
-            out = chain(rows, w_out, x, norm_w, eps, gate_up, down)
-            if out is not None:
-                return x, out
-            a = ctx.ops.linear(rows, w_out)
+            chain = getattr(ops, "decode_chain", None) if self.chain else None
+            if chain is not None:
+                norm_w, eps = self.norm2.rms_params()
+                gate_up, down = self.feed_forward.gated_weights()
+                out = chain(rows, w_out, x, norm_w, eps, gate_up, down)
+                if out is not None:
+                    return x, out
+            a = ops.linear(rows, w_out, defer=True) if defer else ops.linear(rows, w_out)
         else:
             a = self.mixer.forward(h, ctx, cache, self.position, owns_cache)
         h = self.norm2.forward(x, a, ctx)
+        if self.open_ffn and defer:
+            rows, w_out = self.feed_forward.forward_open(h, ctx)
+            return x, ops.linear(rows, w_out, defer=True)
         return x, self.feed_forward.forward(h, ctx)

@@ -26,8 +26,12 @@ class SwiGLU(Part):
         self.down = tensors.pop("down_proj")
 
     def forward(self, h, ctx):
-        gu = ctx.ops.linear(h, self.gate_up)
-        return ctx.ops.linear(ctx.ops.swiglu(gu), self.down)
+        rows, w = self.forward_open(h, ctx)
+        return ctx.ops.linear(rows, w)
+
+    def forward_open(self, h, ctx):
+        """Everything but the last product: (silu(gate) * up, down weight)."""
+        return ctx.ops.swiglu(ctx.ops.linear(h, self.gate_up)), self.down
 
     def gated_weights(self):
         return self.gate_up, self.down

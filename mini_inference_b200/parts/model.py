@@ -38,6 +38,8 @@ class DecoderModel:
                         raise KeyError(f"the layer's weight_names has no entry for '{key}'")
                     self._owned.append((names[key], ws, part))
         self.final_norm = build_part("norm", spec.final_norm)
+        norms = [n for b in self.blocks for n in (b.norm1, b.norm2)] + [self.final_norm]
+        self._norms_accept_deferred = all(getattr(n, "accepts_deferred", False) for n in norms)
         for ws in self.final_norm.weight_specs():
             self._owned.append((spec.final_norm_name, ws, self.final_norm))
         self.embedding = None
@@ -97,6 +99,7 @@ class DecoderModel:
         """caches[i]: LayerCache of execution step i.  Returns float32 logits for
         ctx.batch.logit_rows, or None when no row wants logits."""
         b, ops = ctx.batch, ctx.ops
+        ctx.defer_ok = self._norms_accept_deferred and getattr(ops, "deferred", False)
         x = ops.embedding(b.token_ids, self.embedding)
         for position in self._positions.values():
             x = position.on_embedding(x, ctx)

@@ -8,6 +8,7 @@ from .base import Part, WeightSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    accepts_deferred = True      # delta goes to the kernel namespace untouched
     def __init__(self, spec):
         super().__init__(spec)
         self.size = int(spec.get("size"))

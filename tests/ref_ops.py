@@ -27,7 +27,7 @@ class TorchRefOps:
         y = (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
         return (y.float() * weight.float()).to(x.dtype)
 
-    def linear(self, x, w, out_dtype=None):
+    def linear(self, x, w, out_dtype=None, defer=False):
         return (x.float() @ w.float().T).to(out_dtype or x.dtype)
 
     def swiglu(self, gate_up):

@@ -395,3 +395,36 @@ def test_decode_chain_refuses(chain_ops):
     assert ops.decode_chain(mk(17, 128), mk(192, 128), mk(17, 192), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
     assert ops.decode_chain(mk(4, 128), mk(200, 128), mk(4, 200), mk(200), 1e-5, mk(640, 200), mk(200, 320)) is None
     assert ops.decode_chain(mk(4, 128), mk(192, 128), mk(4, 192).float(), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 32])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (2560, 9728), (100, 64), (516, 192), (19456, 2560)])
+def test_deferred_sums(ops, M, N, K):
+    """A few-row product left as partial sums: adding them up gives the bits the GEMM's own fix-up stores, and the
+    residual-add + norm that reads them directly matches the separate kernels."""
+    from mini_inference_b200.ops import DeferredSum
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16).to(DEV)
+    res = (torch.randn(M, N, generator=g) * 2).to(torch.bfloat16).to(DEV)
+    nw = (torch.rand(N, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    saved = ops._linear_choice
+    ops._linear_choice = {(ops._row_bucket(M), N, K): "stream"}
+    try:
+        plain_out = ops.linear(x, w)
+        lazy = ops.linear(x, w, defer=True)
+        assert isinstance(lazy, DeferredSum) and lazy.shape == (M, N)
+        assert torch.equal(ops.materialize(lazy), plain_out)
+        x1, x2 = res.clone(), res.clone()
+        y1 = ops.add_rmsnorm(x1, lazy, nw, 1e-5)
+        y2 = ops.add_rmsnorm(x2, plain_out, nw, 1e-5)
+        ops.check_errors()
+        assert torch.equal(x1, x2)
+        close(y1, y2, torch.bfloat16)
+        # a reader that normalises selected rows only gets the product itself
+        rows = torch.tensor([M - 1, 0], dtype=torch.int32, device=DEV)
+        x3 = res.clone()
+        close(ops.add_rmsnorm(x3, lazy, nw, 1e-5, rows), ops.add_rmsnorm(res.clone(), plain_out, nw, 1e-5, rows), torch.bfloat16)
+        assert torch.equal(x3, res)
+    finally:
+        ops._linear_choice = saved
