@@ -46,6 +46,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 constexpr int DEC_WARPS = 4;
 
+// Optional work of the kernel before this one, done in this kernel's preamble when every row of the step is a decoded
+// token: per-head RMSNorm of q and k, rotation, and the write of the new token's k and v into the pages
+// (csrc/qk_rope_cache.cu, same arithmetic and rounding).  qkv == nullptr: q arrives finished and the cache is complete.
+struct FusedQK {
+    const __nv_bfloat16* qkv;           // [T, (H + 2 KV) D] raw projections
+    const __nv_bfloat16* q_w;           // [D] or null (no norm)
+    const __nv_bfloat16* k_w;
+    const float* inv_freq;              // [D / 2] or null (no rotation)
+    const int* positions;               // [T]
+    const int* slots;                   // [T] cache position of each token: page * page_size + offset
+    __nv_bfloat16* k_out;               // the caches to write the new token into; null: the layer reads another's cache
+    __nv_bfloat16* v_out;
+    float eps;
+};
+
 constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per warp
 
 // BULK = false: K/V go from the pages straight into registers (one block ahead).
@@ -63,7 +78,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
-                       float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word) {
+                       float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word,
+                       const FusedQK fq) {
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
@@ -98,6 +114,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     uint4* q_frag = reinterpret_cast<uint4*>(smem_bytes + FRONT);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bytes + FRONT + (D / 16) * 32 * 16);
     unsigned char* ring = smem_bytes + warp * (DEC_STAGES * 2 * TILE);
+    // fused q/k preparation: the group's finished queries [16][D] and the new token's key and value
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_bytes + FRONT + (D / 16) * 32 * 16 + 128);
+    __nv_bfloat16* knew = qs + 16 * D;
+    __nv_bfloat16* vnew = knew + D;
+    const int blk_new = (len - 1) / 16;
+    const bool writes_new = BULK && fq.qkv != nullptr && fq.k_out != nullptr && blk_new >= b0 && blk_new < b1;
     const uint32_t bar0 = sm100::smem_u32(bars + warp * DEC_STAGES);
     if (BULK && lane == 0) {
         for (int st = 0; st < DEC_STAGES; ++st) sm100::mbar_init(bar0 + 8 * st, 1);
@@ -128,8 +150,66 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             issue(b0 + warp + primed * DEC_WARPS, primed);
         pdl_wait();
     }
+    if (BULK && fq.qkv != nullptr) {
+        constexpr int EPL = D / 32;                        // elements per lane: one head spans the warp
+        const int heads = H + 2 * KV, d0 = lane * EPL;
+        const bool second = d0 >= D / 2;
+        const int i0 = second ? d0 - D / 2 : d0;
+        const __nv_bfloat16* row = fq.qkv + (size_t)tok * heads * D;
+        float cs[EPL], sn[EPL];
+        if (fq.inv_freq) {
+            const float pos = (float)fq.positions[tok];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) sincosf(pos * fq.inv_freq[i0 + e], &sn[e], &cs[e]);
+        }
+        auto load_head = [&](const __nv_bfloat16* src, float* x) {
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) load2(src + d0 + e, x[e], x[e + 1]);
+        };
+        auto store_head = [&](__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) store2(dst + d0 + e, v[e], v[e + 1]);
+        };
+        auto norm_rope = [&](const float* x, const __nv_bfloat16* w, float* o) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) ss += x[e] * x[e];
+            const float rstd = rsqrtf(warp_sum(ss) / (float)D + fq.eps);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const float n = w ? round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(x[e] * rstd) * __bfloat162float(w[d0 + e])) : x[e];
+                const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+                o[e] = fq.inv_freq ? (second ? n * cs[e] + partner * sn[e] : n * cs[e] - partner * sn[e]) : n;
+            }
+        };
+        for (int r = warp; r < 16; r += DEC_WARPS) {
+            float x[EPL], o[EPL];
+            if (r < G) {
+                load_head(row + (size_t)(kvh * G + r) * D, x);
+                norm_rope(x, fq.q_w, o);
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) o[e] = 0.f;
+            }
+            store_head(qs + r * D, o);
+        }
+        if (writes_new && warp == DEC_WARPS - 1) {         // this block's range holds the new token: its key and value
+            const int slot = fq.slots[tok];
+            const size_t at = ((size_t)((slot / ps) * KV + kvh) * ps + (slot % ps)) * D;
+            float x[EPL], o[EPL];
+            load_head(row + (size_t)(H + kvh) * D, x);
+            norm_rope(x, fq.k_w, o);
+            store_head(knew, o);
+            store_head(fq.k_out + at, o);
+            load_head(row + (size_t)(H + KV + kvh) * D, x);
+            store_head(vnew, x);
+            store_head(fq.v_out + at, x);
+        }
+        __syncthreads();
+    }
     if (warp == 0) {
-        const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
+        const bool prepared = BULK && fq.qkv != nullptr;
+        const __nv_bfloat16* qrow = prepared ? qs : q + (size_t)tok * q_stride + (size_t)kvh * G * D;
 #pragma unroll
         for (int j = 0; j < KS / 2; ++j) {
             uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
@@ -203,7 +283,15 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         if (BULK) {
             const int st = nth % DEC_STAGES;
             if (!sm100::mbar_wait(bar0 + 8 * st, (nth / DEC_STAGES) & 1)) { if (lane == 0) atomicExch(error_word, 31); break; }
-            const unsigned char* tile = ring + st * 2 * TILE;
+            unsigned char* tile = ring + st * 2 * TILE;
+            if (writes_new && blk == blk_new) {
+                // the tile came from the pages while this block was writing the new token there: put its row in place
+                const int r = (len - 1) % 16, piece = lane & 15;
+                if (piece < D / 8)
+                    *reinterpret_cast<uint4*>(tile + (lane < 16 ? 0 : TILE) + (piece >> 3) * 2048 + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) =
+                        *reinterpret_cast<const uint4*>((lane < 16 ? knew : vnew) + piece * 8);
+                __syncwarp();
+            }
             frag_k_sw(tile);
             frag_v_sw(tile + TILE);
             __syncwarp();
@@ -367,6 +455,14 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                       int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream);
 
+MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                    float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                    const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                    int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                    int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
+                                    const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
+                                    const int* slots, int write_cache, float eps, cudaStream_t stream);
+
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                  const int* seg_q_start, const int* seg_kv_len, const int* block_table,
@@ -415,7 +511,31 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                       int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream) {
+    return mi_attn_decode_mma_qk(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode, seg_q_start,
+                                 seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale, window, merge_counters,
+                                 error_word, cache_pages, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0.f, stream);
+}
+
+// The staged variant with the work of mi_qk_norm_rope_cache done in its preamble, for steps whose rows are all decoded
+// tokens: qkv [num rows, (H + 2 KV) D] raw projections (q is ignored), q_w / k_w bfloat16 [D] or null, inv_freq float32
+// [D / 2] or null, positions and slots per row; write_cache = 0 when the layer reads another layer's cache (k, v unused).
+// qkv == null: exactly mi_attn_decode_mma_bulk.
+MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                    float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                    const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                    int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                    int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
+                                    const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
+                                    const int* slots, int write_cache, float eps, cudaStream_t stream) {
     if (num_decode == 0) return 0;
+    if (qkv != nullptr && (error_word == nullptr || ((uintptr_t)qkv % 16))) return -2;
+    FusedQK fq = {};
+    if (qkv != nullptr) {
+        fq.qkv = (const __nv_bfloat16*)qkv; fq.q_w = (const __nv_bfloat16*)q_w; fq.k_w = (const __nv_bfloat16*)k_w;
+        fq.inv_freq = inv_freq; fq.positions = positions; fq.slots = slots; fq.eps = eps;
+        fq.k_out = write_cache ? (__nv_bfloat16*)k_cache : nullptr;
+        fq.v_out = write_cache ? (__nv_bfloat16*)v_cache : nullptr;
+    }
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
     const bool bulk = error_word != nullptr;
@@ -430,7 +550,7 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
     const size_t ring_bytes = bulk ? (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 : 0;
     const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
-                        (bulk ? 1024 : 0);
+                        (bulk ? 1024 + 128 + 18 * D * 2 : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LAUNCH(DD, BB) do { \
         static bool configured = false; \
@@ -442,7 +562,7 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
         return (int)launch_pdl(attn_decode_mma_kernel<DD, BB>, grid, dim3(DEC_WARPS * 32), smem, stream, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
-            H, KV, ps, scale_log2, window, merge_counters, error_word); } while (0)
+            H, KV, ps, scale_log2, window, merge_counters, error_word, fq); } while (0)
     if (D == 128) { if (bulk) LAUNCH(128, true); else LAUNCH(128, false); }
     else { if (bulk) LAUNCH(64, true); else LAUNCH(64, false); }
 #undef LAUNCH

@@ -52,9 +52,6 @@ class GQAAttention(Part):
         ops = ctx.ops
         meta = ctx.batch.groups[cache.group]
         qkv = ops.linear(h, self.qkv)
-        q = ops.qk_norm_rope_cache(
-            qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
-            position.rotary_inv_freq(), meta, cache.k if owns_cache else None,
-            cache.v if owns_cache else None)
-        o = ops.paged_attention(q, cache.k, cache.v, meta, self.H, self.KV, self.D, self.scale, self.window)
+        o = ops.qk_attention(qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
+                             position.rotary_inv_freq(), meta, cache.k, cache.v, owns_cache, self.scale, self.window)
         return o, self.o

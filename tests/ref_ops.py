@@ -65,6 +65,11 @@ class TorchRefOps:
             v_cache[page, :, off, :] = v
         return q.reshape(T, H * D)
 
+    def qk_attention(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache, owns_cache, scale, window):
+        q = self.qk_norm_rope_cache(qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta,
+                                    k_cache if owns_cache else None, v_cache if owns_cache else None)
+        return self.paged_attention(q, k_cache, v_cache, meta, H, KV, D, scale, window)
+
     # ---------------------------------------------------------------- attention over the pages
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
         T = q.shape[0]

@@ -428,3 +428,43 @@ def test_deferred_sums(ops, M, N, K):
         assert torch.equal(x3, res)
     finally:
         ops._linear_choice = saved
+
+
+@pytest.mark.parametrize("H,KV,D,page", [(32, 8, 128, 16), (8, 8, 64, 16), (12, 1, 128, 32), (16, 1, 64, 16), (4, 4, 64, 32),
+                                         (6, 2, 128, 16)])
+@pytest.mark.parametrize("window", [None, 29])
+def test_decode_attention_with_fused_qk(ops, H, KV, D, page, window):
+    """Only decoded tokens in the step: q/k norm, rotation and the cache write inside the attention kernel give the
+    same rows and the same cache as the separate kernel (new tokens at a page's first and last place, first tokens of
+    a request, several splits)."""
+    g = torch.Generator().manual_seed(13)
+    segs = [(150, 1), (31, 1), (0, 1), (299, 1), (page - 1, 1), (page, 1), (16, 1), (15, 1), (63, 1)]
+    meta = make_meta(page, segs, 200, seed=4)
+    T = meta.num_tokens
+    qkv = torch.randn(T, (H + 2 * KV) * D, generator=g).to(torch.bfloat16).to(DEV)
+    qw = (torch.rand(D, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    kw = (torch.rand(D, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(DEV)
+    kc0 = torch.randn(201, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    vc0 = torch.randn(201, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    for use_norm, use_rope, owns in ((True, True, True), (False, True, True), (True, False, True), (True, True, False)):
+        a = (qw, kw) if use_norm else (None, None)
+        f = inv_freq if use_rope else None
+        for splits in (None, 1, 3):
+            res = []
+            for fuse in (False, True):
+                kc, vc = kc0.clone(), vc0.clone()
+                saved = ops.fuse_qk
+                ops.fuse_qk, ops.force_splits = fuse, splits
+                before = ops.launches
+                try:
+                    out = ops.qk_attention(qkv.clone(), H, KV, D, *a, 1e-6, f, meta, kc, vc, owns, D ** -0.5, window)
+                finally:
+                    ops.fuse_qk, ops.force_splits = saved, None
+                res.append((out, kc, vc, ops.launches - before))
+                ops.check_errors()
+            (o1, k1, v1, n1), (o2, k2, v2, n2) = res
+            assert n2 == n1 - 1                            # one launch less
+            assert torch.equal(k1, k2) and torch.equal(v1, v2)
+            close(o2, o1, torch.bfloat16, scale=o1.float().abs().max())
+            assert (o2.float() - o1.float()).abs().max() <= 2e-2 * o1.float().abs().max()
