@@ -468,3 +468,30 @@ def test_decode_attention_with_fused_qk(ops, H, KV, D, page, window):
             assert torch.equal(k1, k2) and torch.equal(v1, v2)
             close(o2, o1, torch.bfloat16, scale=o1.float().abs().max())
             assert (o2.float() - o1.float()).abs().max() <= 2e-2 * o1.float().abs().max()
+
+
+@pytest.mark.parametrize("H,KV,D,page", [(32, 8, 128, 16), (8, 2, 64, 64), (16, 1, 128, 256)])
+@pytest.mark.parametrize("window", [None, 1000])
+def test_decode_attention_long_context(ops, H, KV, D, page, window):
+    """Decoded tokens at contexts of thousands of keys (many ring revolutions, many splits, the merge), requests of
+    very different lengths in one launch, one far key that stands out."""
+    g = torch.Generator().manual_seed(21)
+    segs = [(4099, 1), (8999, 1), (17, 1), (1023, 1), (1024, 1), (0, 1)]
+    pages = sum((p + 1 + page - 1) // page for p, _ in segs) + 2
+    meta = make_meta(page, segs, pages, seed=6)
+    T = meta.num_tokens
+    q = torch.randn(T, H * D, generator=g).to(torch.bfloat16).to(DEV)
+    kc = torch.randn(pages + 1, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    vc = torch.randn(pages + 1, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
+    far = 5000 if window is None else 8999 - 700
+    kc[meta.block_table[1, far // page].long(), :, far % page, :] *= 4.0
+    want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+    for bulk in (True, False):
+        for splits in (None, 5):
+            ops.bulk_decode, ops.force_splits = bulk, splits
+            try:
+                got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
+            finally:
+                ops.bulk_decode, ops.force_splits = True, None
+            ops.check_errors()
+            close(got, want, torch.bfloat16)
