@@ -46,6 +46,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 constexpr int DEC_WARPS = 4;
 
+// thread-block cluster: the splits of one (request, kv head) can be one cluster and merge through shared memory
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* local, uint32_t rank) {     // the same variable in block `rank`'s shared memory
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Optional work of the kernel before this one, done in this kernel's preamble when every row of the step is a decoded
 // token: per-head RMSNorm of q and k, rotation, and the write of the new token's k and v into the pages
 // (csrc/qk_rope_cache.cu, same arithmetic and rounding).  qkv == nullptr: q arrives finished and the cache is complete.
@@ -79,7 +96,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
                        float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word,
-                       const FusedQK fq) {
+                       const FusedQK fq, int cluster_merge) {
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
@@ -106,6 +123,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     constexpr int MERGE_BYTES = DEC_WARPS * 16 * (D + 2) * 4;
     constexpr int RING_BYTES = BULK ? DEC_WARPS * DEC_STAGES * 2 * TILE : 0;
     constexpr int FRONT = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;   // the merge scratch re-uses the ring
+    constexpr int CLUSTER_OFF = (MERGE_BYTES + 1023) / 1024 * 256;               // (floats) this split's result, after the scratch
     unsigned char* smem_bytes = reinterpret_cast<unsigned char*>(smem);
     if (BULK) {                                            // swizzle atoms are 1 KB
         smem_bytes = (unsigned char*)(((uintptr_t)smem_bytes + 1023) & ~(uintptr_t)1023);
@@ -396,11 +414,44 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         const int h = kvh * G + row;
         if (S == 1) {
             out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(val);
+        } else if (BULK && cluster_merge) {
+            float* cpart = smem + CLUSTER_OFF;             // [16][D] this split's rows, then [16] their log-sum-exp
+            cpart[idx] = val;
+            if (d == 0) cpart[16 * D + row] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
         } else {
             const size_t pi = ((size_t)blockIdx.x * H + h) * S + s;
             o_part[pi * D + d] = val;
             if (d == 0) lse_part[pi] = den > 0.f ? (mx + log2f(den)) * 0.6931471805599453f : -INFINITY;
         }
+    }
+    if (BULK && cluster_merge && S > 1) {
+        // The S splits of this (request, kv head) are one cluster: split 0 reads the others' rows through distributed
+        // shared memory and writes the result (no partial sums in global memory, no atomic, no fence);
+        // out = sum_s e^(lse_s - max) o_s / sum_s e^(lse_s - max), splits added in index order.
+        cluster_sync();
+        if (cluster_rank() == 0) {
+            const float* cpart = smem + CLUSTER_OFF;
+            for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+                const int row = idx / D, d = idx % D, h = kvh * G + row;
+                float l[8], v[8], mx = -INFINITY;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    l[r] = r < S ? ld_cluster(cpart + 16 * D + row, r) : -INFINITY;
+                    v[r] = r < S ? ld_cluster(cpart + idx, r) : 0.f;
+                    mx = fmaxf(mx, l[r]);
+                }
+                float num = 0.f, den = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float w = expf(l[r] - mx);
+                    den += w;
+                    num += w * v[r];
+                }
+                out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(num / den);
+            }
+        }
+        cluster_sync();                                    // the others' shared memory stays until split 0 has read it
+        return;
     }
     if (S == 1 || merge_counters == nullptr) return;
 
@@ -461,7 +512,7 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
                                     int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                     int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
                                     const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
-                                    const int* slots, int write_cache, float eps, cudaStream_t stream);
+                                    const int* slots, int write_cache, float eps, int cluster_merge, cudaStream_t stream);
 
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
@@ -513,20 +564,21 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream) {
     return mi_attn_decode_mma_qk(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode, seg_q_start,
                                  seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale, window, merge_counters,
-                                 error_word, cache_pages, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0.f, stream);
+                                 error_word, cache_pages, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0.f, 0, stream);
 }
 
 // The staged variant with the work of mi_qk_norm_rope_cache done in its preamble, for steps whose rows are all decoded
 // tokens: qkv [num rows, (H + 2 KV) D] raw projections (q is ignored), q_w / k_w bfloat16 [D] or null, inv_freq float32
 // [D / 2] or null, positions and slots per row; write_cache = 0 when the layer reads another layer's cache (k, v unused).
-// qkv == null: exactly mi_attn_decode_mma_bulk.
+// qkv == null: exactly mi_attn_decode_mma_bulk.  cluster_merge != 0: with 2..8 splits the splits of a (request, kv head) are
+// launched as one thread-block cluster and merged through distributed shared memory (o_part, lse_part, merge_counters unused).
 MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                     float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                     const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                     int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                     int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
                                     const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
-                                    const int* slots, int write_cache, float eps, cudaStream_t stream) {
+                                    const int* slots, int write_cache, float eps, int cluster_merge, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if (qkv != nullptr && (error_word == nullptr || ((uintptr_t)qkv % 16))) return -2;
     FusedQK fq = {};
@@ -552,6 +604,7 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
     const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
                         (bulk ? 1024 + 128 + 18 * D * 2 : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const int use_cluster = (error_word != nullptr && cluster_merge && splits >= 2 && splits <= 8) ? 1 : 0;
 #define LAUNCH(DD, BB) do { \
         static bool configured = false; \
         if (!configured && smem > 48 * 1024) { \
@@ -559,10 +612,18 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
-        return (int)launch_pdl(attn_decode_mma_kernel<DD, BB>, grid, dim3(DEC_WARPS * 32), smem, stream, kmap, vmap, \
+        cudaLaunchConfig_t cfg = {}; \
+        cfg.gridDim = grid; cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
+        cudaLaunchAttribute attr[2]; \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; \
+        attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0; \
+        attr[1].id = cudaLaunchAttributeClusterDimension; \
+        attr[1].val.clusterDim.x = 1; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = splits; \
+        cfg.attrs = attr; cfg.numAttrs = use_cluster ? 2 : 1; \
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
-            H, KV, ps, scale_log2, window, merge_counters, error_word, fq); } while (0)
+            H, KV, ps, scale_log2, window, merge_counters, error_word, fq, use_cluster); } while (0)
     if (D == 128) { if (bulk) LAUNCH(128, true); else LAUNCH(128, false); }
     else { if (bulk) LAUNCH(64, true); else LAUNCH(64, false); }
 #undef LAUNCH

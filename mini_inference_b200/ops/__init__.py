@@ -87,6 +87,8 @@ class CudaOps:
         # MI_BULK_DECODE=0 selects the register-streaming variant
         self.bulk_decode = os.environ.get("MI_BULK_DECODE", "1") == "1"
         self.fused_merge = True              # the last split block to finish merges the splits (no merge launch)
+        # 2..8 splits of a (request, kv head): one thread-block cluster, merged through distributed shared memory
+        self.cluster_merge = os.environ.get("MI_CLUSTER_MERGE", "1") == "1"
         # q/k norm + rotation + cache write inside the decode attention kernel's preamble (one launch less per layer).
         # Measured no faster (3.30 vs 3.30 ms at batch 8, 2.78 vs 2.73 ms at batch 1): the separate kernel's time is
         # hidden by programmatic launch (attention requests its first K/V tiles while it runs), the preamble's is not.
@@ -479,8 +481,9 @@ class CudaOps:
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
                 meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
                 H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), _p(err_word), k_cache.shape[0],
-                _p(qkv), _p(q_w), _p(k_w), _p(inv_freq), _p(meta.positions), _p(meta.slots), int(bool(owns)),
-                _c.c_float(eps), self._stream()), "attn_decode_mma")
+                _p(qkv), _p(q_w), _p(k_w), _p(inv_freq), _p(meta.positions if fused is not None else None),
+                _p(meta.slots if fused is not None else None), int(bool(owns)),
+                _c.c_float(eps), int(self.cluster_merge), self._stream()), "attn_decode_mma")
             self.launches += 1
             if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,

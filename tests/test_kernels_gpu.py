@@ -262,9 +262,10 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
     # make one far key of the long decode stand out, so that a lost or misplaced key shows
     kc[meta.block_table[5, 2].long(), :, 3, :] *= 4.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-    for fast, fused in ((True, True), (True, False), (False, False)):
+    # splits merged by a cluster through shared memory / by the last block to finish / by a merge kernel / generic kernels
+    for fast, fused, cluster in ((True, True, True), (True, True, False), (True, False, False), (False, False, False)):
         for splits in (None, 1, 3):
-            ops.force_splits, ops.fast_attention, ops.fused_merge = splits, fast, fused
+            ops.force_splits, ops.fast_attention, ops.fused_merge, ops.cluster_merge = splits, fast, fused, cluster
             ops.tc_attention = splits != 3               # prompt portions: tcgen05 kernel, and the mma.sync kernel
             ops.bulk_decode = splits != 1                # decoded tokens: bulk-copy ring, and register streaming
             try:
@@ -272,7 +273,7 @@ def test_paged_attention(ops, dtype, H, KV, D, page, window):
                 got2 = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)    # counters were left clean
             finally:
                 ops.force_splits, ops.fast_attention, ops.fused_merge, ops.tc_attention = None, True, True, True
-                ops.bulk_decode = True
+                ops.bulk_decode = ops.cluster_merge = True
             close(got, want, dtype)
             assert torch.equal(got, got2)
             ops.check_errors()
@@ -486,12 +487,12 @@ def test_decode_attention_long_context(ops, H, KV, D, page, window):
     far = 5000 if window is None else 8999 - 700
     kc[meta.block_table[1, far // page].long(), :, far % page, :] *= 4.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-    for bulk in (True, False):
-        for splits in (None, 5):
-            ops.bulk_decode, ops.force_splits = bulk, splits
+    for bulk, cluster in ((True, True), (True, False), (False, False)):
+        for splits in (None, 5, 8, 11):
+            ops.bulk_decode, ops.cluster_merge, ops.force_splits = bulk, cluster, splits
             try:
                 got = ops.paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
             finally:
-                ops.bulk_decode, ops.force_splits = True, None
+                ops.bulk_decode, ops.cluster_merge, ops.force_splits = True, True, None
             ops.check_errors()
             close(got, want, torch.bfloat16)
