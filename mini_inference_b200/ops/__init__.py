@@ -142,6 +142,25 @@ class CudaOps:
         self.launches += 1
         return y
 
+    def gated_linear(self, x, w):
+        """silu(g) * u with [g | u] = x @ w.T (w = [gate rows | up rows]).  Many rows: one tcgen05 kernel whose epilogue
+        applies the activation (csrc/gemm_tc.cu), so the [M, 2 I] product is never written; otherwise product, then swiglu."""
+        M, K = x.shape
+        inter = w.shape[0] // 2
+        if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            if self._stream_error is None:
+                self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
+                self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
+            act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+            rc = self.lib.mi_gemm_tc_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
+            if rc == 0:
+                self.launches += 1
+                return act
+            if rc != -2:
+                _check(rc, "gemm_tc_swiglu")
+        return self.swiglu(self.linear(x, w))
+
     def materialize(self, value):
         """The bfloat16 tensor behind a DeferredSum (anything else is returned as it is)."""
         if not isinstance(value, DeferredSum):

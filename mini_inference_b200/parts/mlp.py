@@ -31,7 +31,7 @@ class SwiGLU(Part):
 
     def forward_open(self, h, ctx):
         """Everything but the last product: (silu(gate) * up, down weight)."""
-        return ctx.ops.swiglu(ctx.ops.linear(h, self.gate_up)), self.down
+        return ctx.ops.gated_linear(h, self.gate_up), self.down
 
     def gated_weights(self):
         return self.gate_up, self.down

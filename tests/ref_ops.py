@@ -30,6 +30,9 @@ class TorchRefOps:
     def linear(self, x, w, out_dtype=None, defer=False):
         return (x.float() @ w.float().T).to(out_dtype or x.dtype)
 
+    def gated_linear(self, x, w):
+        return self.swiglu(self.linear(x, w))
+
     def swiglu(self, gate_up):
         g, u = gate_up.float().chunk(2, dim=-1)
         return (torch.nn.functional.silu(g) * u).to(gate_up.dtype)

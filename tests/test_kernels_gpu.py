@@ -190,6 +190,25 @@ def test_gemm_tc(ops, M, N, K):
     ops.check_errors()
 
 
+@pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (200, 264, 192), (2048, 9728, 2560), (300, 1000, 640), (129, 40, 128)])
+def test_gemm_tc_swiglu(ops, M, inter, K):
+    """The tcgen05 product whose epilogue applies silu(gate) * up against the separate kernels' arithmetic."""
+    g = torch.Generator().manual_seed(M + inter)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * inter, K, generator=g) * K ** -0.5).to(torch.bfloat16).to(DEV)
+    saved = ops.tc_gemm
+    ops.tc_gemm = True
+    try:
+        before = ops.launches
+        got = ops.gated_linear(x, w)
+        assert ops.launches == before + 1
+    finally:
+        ops.tc_gemm = saved
+    ops.check_errors()
+    ref = TorchRefOps()
+    close(got, ref.swiglu(ref.linear(x, w)), torch.bfloat16)
+
+
 def make_meta(page_size, segs, num_pages, seed, tile=64):
     """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
     shaped like engine.batch.GroupMeta."""
