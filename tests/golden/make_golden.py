@@ -67,4 +67,6 @@ def main(reference_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py PATH_TO_A_CHECKOUT_OF_davidjoyme/mini-inference")
+    main(sys.argv[1])
