@@ -208,7 +208,8 @@ def profile(args, cfg, torch, LLM):
         with open(args.choices) as f:
             llm.ops._linear_choice = {tuple(int(v) for v in k.split(",")): c for k, c in json.load(f).items()}
     else:
-        llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32})
+        llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32},
+                            deferrable=llm.model.deferrable_shapes())
         if args.choices:
             with open(args.choices, "w") as f:
                 json.dump({",".join(str(v) for v in k): c for k, c in llm.ops._linear_choice.items()}, f)

@@ -567,6 +567,29 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                  error_word, cache_pages, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0.f, 0, stream);
 }
 
+// How many clusters of `splits` blocks of the staged kernel the GPU holds at once (0: unknown or none).
+MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
+    if ((D != 64 && D != 128) || splits < 2 || splits > 8) return 0;
+    const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
+                        1024 + 128 + 18 * D * 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, splits); cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e;
+    if (D == 128) {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<128, true>, &cfg);
+    } else {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<64, true>, &cfg);
+    }
+    return e == cudaSuccess ? n : 0;
+}
+
 // The staged variant with the work of mi_qk_norm_rope_cache done in its preamble, for steps whose rows are all decoded
 // tokens: qkv [num rows, (H + 2 KV) D] raw projections (q is ignored), q_w / k_w bfloat16 [D] or null, inv_freq float32
 // [D / 2] or null, positions and slots per row; write_cache = 0 when the layer reads another layer's cache (k, v unused).
@@ -604,7 +627,7 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
     const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
                         (bulk ? 1024 + 128 + 18 * D * 2 : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const int use_cluster = (error_word != nullptr && cluster_merge && splits >= 2 && splits <= 8) ? 1 : 0;
+    int use_cluster = (error_word != nullptr && cluster_merge && splits >= 2 && splits <= 8) ? 1 : 0;
 #define LAUNCH(DD, BB) do { \
         static bool configured = false; \
         if (!configured && smem > 48 * 1024) { \
@@ -615,11 +638,24 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
         cudaLaunchConfig_t cfg = {}; \
         cfg.gridDim = grid; cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
         cudaLaunchAttribute attr[2]; \
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; \
-        attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0; \
-        attr[1].id = cudaLaunchAttributeClusterDimension; \
-        attr[1].val.clusterDim.x = 1; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = splits; \
-        cfg.attrs = attr; cfg.numAttrs = use_cluster ? 2 : 1; \
+        attr[0].id = cudaLaunchAttributeClusterDimension; \
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits; \
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; \
+        attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0; \
+        if (use_cluster) { \
+            /* clusters are placed whole inside one GPC: if they do not all fit at once, some wait for a second wave, */ \
+            /* which costs more than the merge through global memory that the cluster would save */ \
+            static int fit[9] = {0}; \
+            if (fit[splits] == 0) { \
+                cfg.attrs = attr; cfg.numAttrs = 1; \
+                int n = 0; \
+                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB>, &cfg) != cudaSuccess || n < 1) n = -1; \
+                fit[splits] = n; \
+            } \
+            /* (with a margin: blocks of the kernels before and after share the SMs for a moment) */ \
+            if (fit[splits] < 0 || (long long)num_decode * KV * 100 > (long long)fit[splits] * 92) use_cluster = 0; \
+        } \
+        cfg.attrs = use_cluster ? attr : attr + 1; cfg.numAttrs = use_cluster ? 2 : 1; \
         return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \

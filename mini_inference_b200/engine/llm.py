@@ -67,7 +67,8 @@ class LLM:
         self.linear_tuning = None
         if args.cuda_graphs and self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_linear"):
             self.linear_tuning = self.ops.tune_linear(self.model.matrix_weights(),
-                                                      {tuple(self.model.lm_head.shape): torch.float32})
+                                                      {tuple(self.model.lm_head.shape): torch.float32},
+                                                      deferrable=self.model.deferrable_shapes())
         if args.cuda_graphs:
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self.runner, args.max_num_seqs)

@@ -94,6 +94,7 @@ class CudaOps:
         # hidden by programmatic launch (attention requests its first K/V tiles while it runs), the preamble's is not.
         self.fuse_qk = os.environ.get("MI_FUSE_QK", "0") == "1"
         self._merge_counters = None
+        self._cluster_fit = {}
         self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
         self._stream_plans, self._stream_counters, self._stream_error = {}, None, None
         # a few-row product whose only reader is the next residual-add + norm is left as partial sums for that kernel
@@ -237,7 +238,7 @@ class CudaOps:
                 return b
         return 0
 
-    def tune_linear(self, weights, out_dtypes=None, iters=16, min_bytes=256 << 20):
+    def tune_linear(self, weights, out_dtypes=None, iters=16, min_bytes=256 << 20, deferrable=()):
         """Per weight shape and row-count bucket, time this package's few-row kernels against the
         library GEMM on the model's own weights and remember the fastest.  The reference does the
         same kind of start-up timing to choose a weight layout per shape
@@ -266,8 +267,11 @@ class CudaOps:
                             continue
                         self.stream_gemm, self.skinny_gemm = name == "stream", name == "skinny"
                         self.skinny_max_rows, self.skinny_max_cols, self.stream_max_cols = 64, 1 << 30, 1 << 30
-                        times[name] = min(self._time_in_graph(lambda i: self.linear(x, ws[i % len(ws)], out_dtype=od), iters)
-                                          for _ in range(2))
+                        run = lambda i: self.linear(x, ws[i % len(ws)], out_dtype=od)
+                        if name == "stream" and (N, K) in deferrable and self.defer_sums and od in (None, torch.bfloat16):
+                            # these products are read by a norm kernel that adds the partial sums itself
+                            run = lambda i: self._gemm_stream(x, ws[i % len(ws)], torch.bfloat16, defer=True)
+                        times[name] = min(self._time_in_graph(run, iters) for _ in range(2))
                     best = min(times, key=times.get)
                     if times[best] > 0.95 * times["library"]:      # an own kernel has to win clearly
                         best = "library"
@@ -407,21 +411,34 @@ class CudaOps:
         return qkv[:, :H * D]
 
     # ---------------------------------------------------------------- attention over the pages
-    def choose_splits(self, ctas, max_kv_len, per_sm=2):
+    def _cluster_fits(self, D, S, clusters):
+        """Whether `clusters` clusters of S blocks of the staged decode kernel are resident at once, with the margin the
+        kernel itself asks for (clusters are placed whole inside a GPC; a second wave costs more than the merge saves)."""
+        key = (D, S)
+        if key not in self._cluster_fit:
+            self._cluster_fit[key] = int(self.lib.mi_attn_decode_cluster_fit(D, S))
+        return clusters * 100 <= self._cluster_fit[key] * 92
+
+    def choose_splits(self, ctas, max_kv_len, per_sm=2, cluster=False, head_dim=128):
         """Enough blocks to fill the GPU about twice, never more splits than the longest
-        request has 256-key pieces (kernels/paged_attention/decode_triton.py:114-120)."""
+        request has 256-key pieces (kernels/paged_attention/decode_triton.py:114-120).
+        cluster: up to 8 splits can merge through distributed shared memory, which is worth more
+        than finer splits while a split stays within ~1,000 keys (12.5 vs 14.8 us at batch 1, context 4096)."""
         if self.force_splits:
             return self.force_splits
         slots = per_sm * self.NUM_SMS                      # blocks resident at once
         most = max(1, min(math.ceil(max_kv_len / 256), 32))
         if ctas * most <= slots:
-            return most
+            return 8 if cluster and most > 8 and max_kv_len <= 8 * 1024 and self._cluster_fits(head_dim, 8, ctas) else most
         # more blocks than fit at once: take the fewest splits whose last wave is at least 85 % full
         best, best_eff = 1, 0.0
         for S in range(1, most + 1):
             total = ctas * S
             eff = total / (math.ceil(total / slots) * slots)
             if eff >= 0.85:
+                # one split fewer if that lets the splits merge as clusters
+                if cluster and 2 < S <= 8 and not self._cluster_fits(head_dim, S, ctas) and self._cluster_fits(head_dim, S - 1, ctas):
+                    return S - 1
                 return S
             if eff > best_eff:
                 best, best_eff = S, eff
@@ -477,7 +494,8 @@ class CudaOps:
         fast_decode = fast and H // KV <= 16 and meta.page_size % 16 == 0
         if meta.num_decode:
             S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len,
-                                   (2 if self.bulk_decode else 3) if fast_decode else 2)
+                                   (2 if self.bulk_decode else 3) if fast_decode else 2,
+                                   cluster=fast_decode and self.bulk_decode and self.cluster_merge, head_dim=D)
             o_part = lse = None
             if S > 1:
                 o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)

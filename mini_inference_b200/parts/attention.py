@@ -43,6 +43,10 @@ class GQAAttention(Part):
         self.o = tensors.pop("o_proj")
         self.q_norm, self.k_norm = tensors.get("q_norm"), tensors.get("k_norm")
 
+    @property
+    def open_weight(self):
+        return self.o
+
     def forward(self, h, ctx, cache, position, owns_cache=True):
         o, w = self.forward_open(h, ctx, cache, position, owns_cache)
         return ctx.ops.linear(o, w)

@@ -25,7 +25,7 @@ Interfaces
 
 Optional fast-path protocol (a block may use what its parts offer; none has to):
   Mixer        forward_open(h, ctx, cache, position, owns_cache) -> (rows, out_weight)
-                   forward() without its last product: forward == linear(rows, out_weight)
+                   forward() without its last product: forward == linear(rows, out_weight); open_weight names that tensor
   FeedForward  forward_open(h, ctx) -> (rows, out_weight)      the same
   Norm         accepts_deferred = True   when forward hands `delta` to ctx.ops.add_rmsnorm untouched: the block may then
                    give it the result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)

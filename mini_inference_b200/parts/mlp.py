@@ -25,6 +25,10 @@ class SwiGLU(Part):
         self.gate_up = torch.cat([tensors.pop("gate_proj"), tensors.pop("up_proj")], dim=0).contiguous()
         self.down = tensors.pop("down_proj")
 
+    @property
+    def open_weight(self):
+        return self.down
+
     def forward(self, h, ctx):
         rows, w = self.forward_open(h, ctx)
         return ctx.ops.linear(rows, w)

@@ -86,6 +86,19 @@ class DecoderModel:
         out.append(self.lm_head)
         return out
 
+    def deferrable_shapes(self):
+        """(N, K) of the products whose only reader is a norm (the last product of a mixer or feed-forward that offers
+        forward_open), when every norm accepts deferred sums: the kernel namespace may time them accordingly."""
+        if not self._norms_accept_deferred:
+            return frozenset()
+        shapes = set()
+        for block in self.blocks:
+            for part in (block.mixer, block.feed_forward):
+                w = getattr(part, "open_weight", None)
+                if hasattr(part, "forward_open") and isinstance(w, torch.Tensor) and w.dim() == 2:
+                    shapes.add((w.shape[0], w.shape[1]))
+        return frozenset(shapes)
+
     # ---------------------------------------------------------------- cache needs
     def cache_needs(self):
         """Per execution step: the mixer's need, or None when the step reads another's cache."""
