@@ -280,10 +280,13 @@ def main():
         return profile(args, cfg, torch, LLM)
     llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
               kv_cache_tokens=kv_tokens, kv_watermark=0.0, max_num_seqs=max(64, args.batch), max_model_len=args.ctx,
-              max_batched_tokens=4096, cuda_graphs=True)
+              max_batched_tokens=4096, cuda_graphs=False)
 
     with ClockSampler() as clocks:
+        # the prompt step first, then the start-up work of the decode path (kernel timing, graph capture): seconds of
+        # back-to-back GEMMs put the GPU under its power cap, and the peak this step is compared with is a burst figure
         pre_ms = prefill(llm, torch, 2048, vocab, warmup=3, reps=5)
+        llm.enable_cuda_graphs()
         main_run = decode_device(llm, torch, args.batch, args.ctx, args.steps, args.warmup, vocab)
         clock_summary = clocks.summary(*main_run["t"])
         e2e = decode_e2e(llm, torch, args.batch, args.ctx, args.steps, args.warmup, vocab)

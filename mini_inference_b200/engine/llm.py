@@ -65,20 +65,28 @@ class LLM:
         self.eos_ids = set(self.model.spec.eos_token_ids)
         self.graphs = None
         self.linear_tuning = None
-        if args.cuda_graphs and self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_linear"):
-            self.linear_tuning = self.ops.tune_linear(self.model.matrix_weights(),
-                                                      {tuple(self.model.lm_head.shape): torch.float32},
-                                                      deferrable=self.model.deferrable_shapes())
         if args.cuda_graphs:
-            from .graphs import DecodeGraphs
-            self.graphs = DecodeGraphs(self.runner, args.max_num_seqs)
-            self.graphs.capture()
+            self.enable_cuda_graphs()
         self.last_error = None
         self._ahead = None               # (chunks, handle) of a decode step launched but not yet delivered
         # step wall time split by kind (engine/custom_engine.py:69,140-142)
         self.step_time = {"decode": [0, 0.0], "other": [0, 0.0]}
 
     # ---------------------------------------------------------------- setup
+    def enable_cuda_graphs(self):
+        """Time the few-row GEMM kernels on this model's weights and capture the decode graphs (what cuda_graphs=True
+        does at construction; may also be called later, between steps)."""
+        if self.graphs is not None:
+            return
+        if self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_linear"):
+            self.linear_tuning = self.ops.tune_linear(self.model.matrix_weights(),
+                                                      {tuple(self.model.lm_head.shape): torch.float32},
+                                                      deferrable=self.model.deferrable_shapes())
+        from .graphs import DecodeGraphs
+        self.graphs = DecodeGraphs(self.runner, self.args.max_num_seqs)
+        self.graphs.capture()
+        self.args.cuda_graphs = True
+
     def _kv_budget_tokens(self, bytes_per_token: int) -> int:
         """engine/custom_engine.py:105-121: fixed token count, fixed megabytes, or what the GPU
         has left after the weights and a reserve for activations."""
