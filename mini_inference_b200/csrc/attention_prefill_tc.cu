@@ -27,6 +27,12 @@
 using namespace mi;
 using namespace mi::sm100;
 
+__device__ __forceinline__ float max3(float a, float b, float c) {      // one instruction on this architecture
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 #ifdef MI_ATT_TIMING
 // phase counters (clock64 ticks summed over blocks): built only with -DMI_ATT_TIMING, read by mi_attn_tc_timing
 __device__ unsigned long long att_ticks[16];
@@ -204,9 +210,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                     if (!vis) r[c] = 0xff800000u;                     // -inf
                 }
             }
-            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one
+            // maximum with three-input max (four chains); exponent arguments and row sums with the packed
+            // two-float fma/add of this architecture: the softmax warps are bound by instruction issue
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 64; ++c) mxs[c & 3] = fmaxf(mxs[c & 3], __uint_as_float(r[c]));
+            for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mxs[q] = max3(mxs[q], __uint_as_float(r[c + 2 * q]), __uint_as_float(r[c + 2 * q + 1]));
+            }
             const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;   // scale > 0
             // keep the exponent offset unless the maximum grew by more than 2^8: rescaling O is then rare
             float alpha = 1.f;
@@ -219,16 +230,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             }
             const float off = m_ref == -INFINITY ? 0.f : m_ref;
             uint32_t pk[32];
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            const float2 scale2 = make_float2(scale_log2, scale_log2), noff2 = make_float2(-off, -off);
+            float2 sums[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * c]), scale_log2, -off));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * c + 1]), scale_log2, -off));
-                sums[c & 3] += p0 + p1;
-                __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                const float2 arg = __ffma2_rn(make_float2(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1])), scale2, noff2);
+                const float2 p = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                sums[c & 3] = __fadd2_rn(sums[c & 3], p);
+                __nv_bfloat162 hh = __floats2bfloat162_rn(p.x, p.y);
                 pk[c] = *reinterpret_cast<uint32_t*>(&hh);
             }
-            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            const float2 s01 = __fadd2_rn(sums[0], sums[1]), s23 = __fadd2_rn(sums[2], sums[3]);
+            const float sum = (s01.x + s01.y) + (s23.x + s23.y);
             l += sum;
             tmem_st32(lane_addr + s_col, pk);                  // P takes the place of the scores it came from
             TICK(t2);
