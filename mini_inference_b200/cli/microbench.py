@@ -5,6 +5,7 @@ bench/micro/bench_attention.py (:61-167: paged decode attention over batch x con
 
     python -m mini_inference_b200.cli.microbench gemm      [--rows 1,8,64] [--size 4b]
     python -m mini_inference_b200.cli.microbench attention [--batch 1,8,64] [--ctx 4096]
+    python -m mini_inference_b200.cli.microbench chain     [--rows 8]    (the one-kernel block tail against its parts)
 
 Each line: kernel, shape, microseconds (CUDA events, after warm-up), GB/s of the bytes the
 kernel has to read, and that as a share of the measured copy bandwidth."""
@@ -112,9 +113,53 @@ def bench_attention(args, ops, peak):
         del kv
 
 
+def bench_chain(args, ops, peak):
+    """The optional one-kernel block tail (out-projection, norm, gated feed-forward) against the separate kernels, and,
+    when the library was built with -DMI_CHAIN_TIMING, the time stamps of its phases (min / median / max over blocks)."""
+    import ctypes
+    cfg = SIZES[args.size]
+    h, q_dim, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["intermediate_size"]
+    layers = max(2, -(-args.rotate_mb * 2 ** 20 // ((h * q_dim + 3 * h * inter) * 2)))
+    g = torch.Generator().manual_seed(1)
+    mk = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(torch.bfloat16).cuda()
+    ws = [(mk(h, q_dim, scale=q_dim ** -0.5), mk(2 * inter, h, scale=h ** -0.5), mk(h, inter, scale=inter ** -0.5)) for _ in range(layers)]
+    nw = torch.ones(h, dtype=torch.bfloat16, device="cuda")
+    nbytes = (h * q_dim + 3 * h * inter) * 2
+    for M in args.rows:
+        attn, x = mk(M, q_dim), mk(M, h)
+
+        def parts(i):
+            w_o, w_gu, w_d = ws[i % layers]
+            y = ops.add_rmsnorm(x, ops.linear(attn, w_o, defer=True), nw, 1e-6)
+            return ops.linear(ops.swiglu(ops.linear(y, w_gu)), w_d)
+        saved = ops.decode_chain_on
+        ops.decode_chain_on = True
+        try:
+            for label, fn in (("one kernel", lambda i: ops.decode_chain(attn, ws[i % layers][0], x, nw, 1e-6, ws[i % layers][1], ws[i % layers][2])),
+                              ("separate", parts)):
+                us = timed(fn, args.iters)
+                print(f"block tail M={M:<3d} {label:11s} {us:8.2f} us {nbytes / us / 1e3:8.1f} GB/s {100 * nbytes / us / 1e3 / peak:5.1f} % of peak",
+                      flush=True)
+            if hasattr(ops.lib, "mi_decode_chain_timing"):
+                import numpy as np
+                ops.decode_chain(attn, ws[0][0], x, nw, 1e-6, ws[0][1], ws[0][2])
+                torch.cuda.synchronize()
+                buf = (ctypes.c_ulonglong * (160 * 16))()
+                ops.lib.mi_decode_chain_timing(buf)
+                st = np.array(buf, dtype=np.uint64).reshape(160, 16)[:ops.NUM_SMS].astype(np.int64)
+                rel = (st - st[:, 0].min()) / 1e3
+                names = ["start", "predecessor done", "p0 rows ready", "p0 first stage", "p0 units done", "p0 reduced",
+                         "p1 rows ready", "p1 first stage", "p1 units done", "p1 activation done", "p2 rows ready",
+                         "p2 first stage", "p2 units done", "p2 reduced", "p0 barrier", "p1 barrier"]
+                for i, name in enumerate(names):
+                    print(f"  {name:20s} min {rel[:, i].min():7.2f}  median {np.median(rel[:, i]):7.2f}  max {rel[:, i].max():7.2f} us")
+        finally:
+            ops.decode_chain_on = saved
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention"])
+    ap.add_argument("what", choices=["gemm", "attention", "chain"])
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--batch", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
@@ -128,7 +173,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    (bench_gemm if args.what == "gemm" else bench_attention)(args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "chain": bench_chain}[args.what](args, ops, peak)
     return 0
 
 
