@@ -181,3 +181,25 @@ def test_run_engine_command_line(tmp_path):
     assert data["summary"]["num_prompts"] == 5 and len(data["runs"]) == 5
     assert all(run["generated_tokens"] == 12 and run["error"] is None for run in data["runs"])
     assert data["summary"]["throughput_tok_s"] > 0 and data["summary"]["graph_replays"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_benchmark_layer_sizes(tmp_path, dtype):
+    """The layer sizes of the benchmark (Qwen3-4B: width 2560, 32/8 heads of 128, feed-forward 9728), two layers and
+    a cut-down vocabulary: whole, the last 32 tokens one by one, and portions, against the plain implementation.  This
+    is where the tensor-core attention, the TMA weight-streaming products and the deferred sums run at their real shapes."""
+    from mini_inference_b200.weights import write_random_model
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 2560, "num_hidden_layers": 2, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728, "vocab_size": 4099, "rope_theta": 1000000.0,
+           "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 4096}
+    d = str(tmp_path / "bench_sizes")
+    write_random_model(cfg, d, seed=3, std=0.02)
+    ids = random_tokens(cfg["vocab_size"], 200, seed=1)
+    want = plain_logits(d, ids)
+    runner = make_engine(d, 16, 64, dtype=dtype, device=DEV)
+    tol = 1e-4 if dtype == "float32" else 5e-2
+    for name, cuts in (("whole", [200]), ("decode", [168] + [1] * 32), ("portions", [90, 7, 2, 64, 35, 2])):
+        got = run_cuts(runner, name, ids, cuts)
+        assert rel_err(got, want) < tol, (name, rel_err(got, want))
+    if hasattr(runner.ops, "check_errors"):
+        runner.ops.check_errors()
