@@ -41,13 +41,20 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // x[t] += bf16(sum of shares); y[t] = rmsnorm(x[t]) * w.  One block per token, one thread per four columns.
+// Blocks beyond the M tokens do no arithmetic: they ask for the first `ahead_bytes` of `ahead` (the weight that the next
+// kernel streams) to be brought into L2.  A decode step has a handful of tokens, so this kernel leaves most SMs idle.
+// They do not wait for the kernel before this one: measured at Qwen3-4B sizes, 8 rows, the requests are worth 2.4 % of a
+// decode step when they go out at once (they fill the product's ramp-down and this kernel's time), 1 % when they wait
+// for it to finish, and more than ~32 MB of them costs what it gains (they then compete with the next product's own loads).
 template <typename WT>
 __global__ void __launch_bounds__(1024)
 deferred_add_rmsnorm_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ ws, const WT* __restrict__ w,
-                            __nv_bfloat16* __restrict__ y, int N, int K, int G, int max_contrib, int tok, float eps) {
+                            __nv_bfloat16* __restrict__ y, int M, int N, int K, int G, int max_contrib, int tok, float eps,
+                            const unsigned char* __restrict__ ahead, long long ahead_bytes) {
     extern __shared__ int shares[];                        // per row tile
     __shared__ float scratch[32];
     pdl_trigger();
+    if (l2_ahead_rides(ahead, ahead_bytes, M)) return;
     const int NKC = K / KC, NRT = (N + TR - 1) / TR;
     const long long U = (long long)NRT * NKC;
     for (int rt = threadIdx.x; rt < NRT; rt += blockDim.x) shares[rt] = shares_of(rt, NKC, U, G);
@@ -105,9 +112,13 @@ __global__ void deferred_reduce_kernel(const float* __restrict__ ws, __nv_bfloat
 
 // x [M, N] bfloat16 (contiguous) += the product held as partial sums in ws; y = rmsnorm(x) * w.  (N, K, grid, max_contrib,
 // tokens_padded) describe the product as mi_gemm_stream_plan did.  N must be a multiple of 4.
+// `ahead` (may be null): a 16-byte aligned tensor that the next kernel reads; its first ahead_bytes are requested into L2.
 MI_EXPORT int mi_deferred_add_rmsnorm(void* x, const float* ws, const void* w, void* y, int M, int N, int K, int grid,
-                                      int max_contrib, int tokens_padded, float eps, int w_dtype, cudaStream_t stream) {
+                                      int max_contrib, int tokens_padded, float eps, int w_dtype, const void* ahead_ptr,
+                                      long long ahead_bytes, cudaStream_t stream) {
     if (M == 0) return 0;
+    const int extra = l2_ahead_extra(ahead_ptr, ahead_bytes, M);
+    const unsigned char* ahead = (const unsigned char*)ahead_ptr;
     if (N % 4 || K % KC || ((uintptr_t)x % 8) || ((uintptr_t)y % 8) || ((uintptr_t)ws % 16)) return -2;
     const int NRT = (N + TR - 1) / TR;
     int threads = ((N / 4 + 31) / 32) * 32;
@@ -115,10 +126,10 @@ MI_EXPORT int mi_deferred_add_rmsnorm(void* x, const float* ws, const void* w, v
     if (threads < 32) threads = 32;
     const size_t smem = (size_t)NRT * sizeof(int);
     if (w_dtype == MI_BF16)
-        return (int)launch_pdl(deferred_add_rmsnorm_kernel<__nv_bfloat16>, dim3(M), dim3(threads), smem, stream, (__nv_bfloat16*)x, ws,
-                               (const __nv_bfloat16*)w, (__nv_bfloat16*)y, N, K, grid, max_contrib, tokens_padded, eps);
-    return (int)launch_pdl(deferred_add_rmsnorm_kernel<float>, dim3(M), dim3(threads), smem, stream, (__nv_bfloat16*)x, ws,
-                           (const float*)w, (__nv_bfloat16*)y, N, K, grid, max_contrib, tokens_padded, eps);
+        return (int)launch_pdl(deferred_add_rmsnorm_kernel<__nv_bfloat16>, dim3(M + extra), dim3(threads), smem, stream, (__nv_bfloat16*)x, ws,
+                               (const __nv_bfloat16*)w, (__nv_bfloat16*)y, M, N, K, grid, max_contrib, tokens_padded, eps, ahead, ahead_bytes);
+    return (int)launch_pdl(deferred_add_rmsnorm_kernel<float>, dim3(M + extra), dim3(threads), smem, stream, (__nv_bfloat16*)x, ws,
+                           (const float*)w, (__nv_bfloat16*)y, M, N, K, grid, max_contrib, tokens_padded, eps, ahead, ahead_bytes);
 }
 
 MI_EXPORT int mi_deferred_reduce(const float* ws, void* out, int M, int N, int K, int grid, int max_contrib, int tokens_padded,

@@ -44,9 +44,11 @@ MI_EXPORT int mi_embedding(const int* ids, const void* table, void* out, int T_,
 // type BEFORE its statistics are taken, as if it had been stored and read back.
 template <typename T, typename WT, int NT>
 __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w,
-                                   T* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+                                   T* __restrict__ y, const int* __restrict__ rows, int hidden, float eps,
+        const unsigned char* __restrict__ ahead, long long ahead_bytes, int work) {
     __shared__ float scratch[32];
     pdl_trigger();
+    if (l2_ahead_rides(ahead, ahead_bytes, work)) return;
     pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
@@ -118,10 +120,12 @@ template <typename T> __device__ __forceinline__ uint4 pack16(const float* v) {
 template <typename T, typename WT, int NT, int VPT>
 __global__ void __launch_bounds__(NT)
 add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
-                       const int* __restrict__ rows, int hidden, float eps) {
+                       const int* __restrict__ rows, int hidden, float eps,
+        const unsigned char* __restrict__ ahead, long long ahead_bytes, int work) {
     __shared__ float scratch[32];
     constexpr int V = Vec16<T>::N;
     pdl_trigger();
+    if (l2_ahead_rides(ahead, ahead_bytes, work)) return;
     pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
@@ -163,9 +167,11 @@ add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT*
 template <typename T, typename WT, int VPT>
 __global__ void __launch_bounds__(128)
 add_rmsnorm_warp_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w, T* __restrict__ y,
-                        const int* __restrict__ rows, int num_rows, int hidden, float eps) {
+                        const int* __restrict__ rows, int num_rows, int hidden, float eps,
+        const unsigned char* __restrict__ ahead, long long ahead_bytes, int work) {
     constexpr int V = Vec16<T>::N;
     pdl_trigger();
+    if (l2_ahead_rides(ahead, ahead_bytes, work)) return;
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -216,8 +222,11 @@ add_rmsnorm_warp_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT
     }
 }
 
-MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
-                             int hidden, float eps, int dtype, int w_dtype, cudaStream_t stream) {
+// ahead (may be null): a 16-byte aligned tensor that the next kernel streams; at few rows extra blocks of this launch ask
+// for its first ahead_bytes to be brought into L2 (l2_ahead_rides in common.cuh).
+MI_EXPORT int mi_add_rmsnorm_ahead(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
+                                   int hidden, float eps, int dtype, int w_dtype, const void* ahead_ptr, long long ahead_bytes,
+                                   cudaStream_t stream) {
     if (num_rows == 0) return 0;
     constexpr int NT = 256;
     const int vw = dtype == MI_BF16 ? 8 : 4;
@@ -225,13 +234,16 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
                      ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)delta % 16 == 0);
     const int nvec = hidden / vw;
     const bool by_warp = vec && num_rows >= 64 && nvec <= 32 * 16;
+    const int work = by_warp ? (num_rows + 3) / 4 : num_rows;
+    const int blocks = work + l2_ahead_extra(ahead_ptr, ahead_bytes, work);
+    const unsigned char* ahead = (const unsigned char*)ahead_ptr;
 #define LAUNCH(T, WT) do { \
-        if (by_warp && nvec <= 32 * 4) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 4>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp && nvec <= 32 * 8) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 8>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp && nvec <= 32 * 12) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 12>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (by_warp) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 16>, dim3((num_rows + 3) / 4), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps); \
-        if (vec) return (int)launch_pdl(add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
-        return (int)launch_pdl(add_rmsnorm_kernel<T, WT, NT>, dim3(num_rows), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps); \
+        if (by_warp && nvec <= 32 * 4) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 4>, dim3(blocks), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps, ahead, ahead_bytes, work); \
+        if (by_warp && nvec <= 32 * 8) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 8>, dim3(blocks), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps, ahead, ahead_bytes, work); \
+        if (by_warp && nvec <= 32 * 12) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 12>, dim3(blocks), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps, ahead, ahead_bytes, work); \
+        if (by_warp) return (int)launch_pdl(add_rmsnorm_warp_kernel<T, WT, 16>, dim3(blocks), dim3(128), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, num_rows, hidden, eps, ahead, ahead_bytes, work); \
+        if (vec) return (int)launch_pdl(add_rmsnorm_vec_kernel<T, WT, NT, (sizeof(T) == 2 ? 4 : 8)>, dim3(blocks), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps, ahead, ahead_bytes, work); \
+        return (int)launch_pdl(add_rmsnorm_kernel<T, WT, NT>, dim3(blocks), dim3(NT), 0, stream, (T*)x, (const T*)delta, (const WT*)w, (T*)y, rows, hidden, eps, ahead, ahead_bytes, work); \
     } while (0)
     if (dtype == MI_BF16 && w_dtype == MI_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == MI_BF16) LAUNCH(__nv_bfloat16, float);
@@ -239,6 +251,11 @@ MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y,
     else return -1;
 #undef LAUNCH
     return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_add_rmsnorm(void* x, const void* delta, const void* w, void* y, const int* rows, int num_rows,
+                             int hidden, float eps, int dtype, int w_dtype, cudaStream_t stream) {
+    return mi_add_rmsnorm_ahead(x, delta, w, y, rows, num_rows, hidden, eps, dtype, w_dtype, nullptr, 0, stream);
 }
 
 // ------------------------------------------------------------------ silu(gate) * up

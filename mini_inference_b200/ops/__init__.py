@@ -74,6 +74,7 @@ class DeferredSum:
 class CudaOps:
     prefill_tile = 64
     deferred = True                          # linear(..., defer=True) may answer with a DeferredSum
+    takes_hints = True                       # add_rmsnorm(..., next_weight=) is understood
     NUM_SMS = 148
 
     def __init__(self, device):
@@ -108,6 +109,10 @@ class CudaOps:
         # a few-row product whose only reader is the next residual-add + norm is left as partial sums for that kernel
         # to add up (no fix-up tail in the GEMM); MI_DEFER_SUMS=0 turns it off
         self.defer_sums = os.environ.get("MI_DEFER_SUMS", "1") == "1"
+        # few rows: the residual-add + norm kernel's idle blocks request the first bytes of the weight that the next
+        # product streams into L2 (MI_L2_AHEAD_MB=0 turns it off)
+        self.l2_ahead_bytes = int(float(os.environ.get("MI_L2_AHEAD_MB", "32")) * (1 << 20))
+        self.l2_ahead_max_rows = 64
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
@@ -132,13 +137,19 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def add_rmsnorm(self, x, delta, weight, eps, rows=None):
+    def add_rmsnorm(self, x, delta, weight, eps, rows=None, next_weight=None):
+        """x += delta (if any), y = rmsnorm(x) * weight.  next_weight: the tensor that the caller's next kernel streams; at
+        few rows the kernel's idle blocks ask for its first bytes to be brought into L2 (a hint, never needed)."""
         hidden = x.shape[-1]
+        ahead, ahead_bytes = None, 0
+        if next_weight is not None and self.l2_ahead_bytes and x.shape[0] <= self.l2_ahead_max_rows and next_weight.is_contiguous():
+            ahead, ahead_bytes = next_weight, min(next_weight.numel() * next_weight.element_size(), self.l2_ahead_bytes)
         if isinstance(delta, DeferredSum):
             if rows is None and x.dtype == torch.bfloat16 and x.is_contiguous() and hidden % 4 == 0 and delta.shape == tuple(x.shape):
                 y = torch.empty_like(x)
                 rc = self.lib.mi_deferred_add_rmsnorm(_p(x), _p(delta.ws), _p(weight), _p(y), delta.M, delta.N, delta.K, delta.grid,
-                                                      delta.max_contrib, delta.tok, _c.c_float(eps), _code(weight.dtype), self._stream())
+                                                      delta.max_contrib, delta.tok, _c.c_float(eps), _code(weight.dtype),
+                                                      _p(ahead), _c.c_longlong(ahead_bytes), self._stream())
                 if rc == 0:
                     self.launches += 1
                     return y
@@ -148,8 +159,9 @@ class CudaOps:
         assert x.is_contiguous() and (delta is None or delta.is_contiguous())
         n = x.shape[0] if rows is None else rows.shape[0]
         y = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
-        _check(self.lib.mi_add_rmsnorm(_p(x), _p(delta), _p(weight), _p(y), _p(rows), n, hidden, _c.c_float(eps),
-                                       _code(x.dtype), _code(weight.dtype), self._stream()), "add_rmsnorm")
+        _check(self.lib.mi_add_rmsnorm_ahead(_p(x), _p(delta), _p(weight), _p(y), _p(rows), n, hidden, _c.c_float(eps),
+                                             _code(x.dtype), _code(weight.dtype), _p(ahead), _c.c_longlong(ahead_bytes),
+                                             self._stream()), "add_rmsnorm")
         self.launches += 1
         return y
 

@@ -32,6 +32,9 @@ Optional fast-path protocol (a block may use what its parts offer; none has to):
                rms_params() -> (weight, eps)   when forward is the plain RMS norm
   FeedForward  gated_weights() -> (gate_up [2I, hidden], down [hidden, I])
                    when forward == linear(silu(g) * u, down) with [g | u] = linear(h, gate_up)
+  Mixer, FeedForward   first_weight -> the tensor that forward() reads first
+  Norm         takes_next_weight = True   when forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the
+                   block names the first weight of the part that follows the norm, and the kernel may request it into L2
 """
 from __future__ import annotations
 
@@ -78,6 +81,7 @@ class StepContext:
     def __init__(self, ops, batch, dtype, device):
         self.ops, self.batch, self.dtype, self.device = ops, batch, dtype, device
         self.defer_ok = False        # set by the model when every reader of a block's outputs accepts deferred sums
+        self.hints_ok = False        # the kernel namespace's add_rmsnorm takes next_weight=
 
 
 class Part:

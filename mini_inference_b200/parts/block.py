@@ -23,10 +23,14 @@ class PreNormBlock(Part):
 
         self.open_mixer = hasattr(mixer, "forward_open")
         self.open_ffn = hasattr(feed_forward, "forward_open")
+        # a norm that takes the hint is told which weight is streamed right after it
+        self.hint1 = getattr(norm1, "takes_next_weight", False) and hasattr(mixer, "first_weight")
+        self.hint2 = getattr(norm2, "takes_next_weight", False) and hasattr(feed_forward, "first_weight")
 
     def forward(self, x, delta, ctx, cache, owns_cache=True):
         ops = ctx.ops
-        h = self.norm1.forward(x, delta, ctx)
+        h = (self.norm1.forward(x, delta, ctx, next_weight=self.mixer.first_weight) if self.hint1
+             else self.norm1.forward(x, delta, ctx))
         defer = ctx.defer_ok                   # the readers of `a` and of the returned delta are norms that accept it
         if self.open_mixer:
             rows, w_out = self.mixer.forward_open(h, ctx, cache, self.position, owns_cache)
@@ -40,7 +44,8 @@ class PreNormBlock(Part):
             a = ops.linear(rows, w_out, defer=True) if defer else ops.linear(rows, w_out)
         else:
             a = self.mixer.forward(h, ctx, cache, self.position, owns_cache)
-        h = self.norm2.forward(x, a, ctx)
+        h = (self.norm2.forward(x, a, ctx, next_weight=self.feed_forward.first_weight) if self.hint2
+             else self.norm2.forward(x, a, ctx))
         if self.open_ffn and defer:
             rows, w_out = self.feed_forward.forward_open(h, ctx)
             return x, ops.linear(rows, w_out, defer=True)

@@ -29,6 +29,10 @@ class SwiGLU(Part):
     def open_weight(self):
         return self.down
 
+    @property
+    def first_weight(self):
+        return self.gate_up
+
     def forward(self, h, ctx):
         rows, w = self.forward_open(h, ctx)
         return ctx.ops.linear(rows, w)

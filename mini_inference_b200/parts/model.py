@@ -113,6 +113,7 @@ class DecoderModel:
         ctx.batch.logit_rows, or None when no row wants logits."""
         b, ops = ctx.batch, ctx.ops
         ctx.defer_ok = self._norms_accept_deferred and getattr(ops, "deferred", False)
+        ctx.hints_ok = getattr(ops, "takes_hints", False)
         x = ops.embedding(b.token_ids, self.embedding)
         for position in self._positions.values():
             x = position.on_embedding(x, ctx)

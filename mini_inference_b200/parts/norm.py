@@ -9,6 +9,8 @@ from .base import Part, WeightSpec, register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Part):
     accepts_deferred = True      # delta goes to the kernel namespace untouched
+    takes_next_weight = True     # and so does the hint about the weight that is read next
+
     def __init__(self, spec):
         super().__init__(spec)
         self.size = int(spec.get("size"))
@@ -21,7 +23,9 @@ class RMSNorm(Part):
     def load(self, tensors, dtype, device):
         self.weight = tensors["weight"]
 
-    def forward(self, x, delta, ctx, rows=None):
+    def forward(self, x, delta, ctx, rows=None, next_weight=None):
+        if next_weight is not None and ctx.hints_ok:
+            return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows, next_weight=next_weight)
         return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows)
 
     def rms_params(self):

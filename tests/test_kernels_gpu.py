@@ -446,6 +446,16 @@ def test_deferred_sums(ops, M, N, K):
         x3 = res.clone()
         close(ops.add_rmsnorm(x3, lazy, nw, 1e-5, rows), ops.add_rmsnorm(res.clone(), plain_out, nw, 1e-5, rows), torch.bfloat16)
         assert torch.equal(x3, res)
+        # the hint about the weight that is read next changes nothing but the kernel's grid: whole tensors, a few
+        # bytes, a size that is no multiple of the request size, a view that starts off a 16-byte boundary
+        odd = torch.randn(5000, generator=g).to(torch.bfloat16).to(DEV)
+        for hint in (w, odd, odd[:4], odd[1:]):
+            x4, x5 = res.clone(), res.clone()
+            close(ops.add_rmsnorm(x4, lazy, nw, 1e-5, next_weight=hint), y1, torch.bfloat16)
+            assert torch.equal(x4, x1)
+            close(ops.add_rmsnorm(x5, plain_out, nw, 1e-5, next_weight=hint), y2, torch.bfloat16)
+            assert torch.equal(x5, x2)
+        ops.check_errors()
     finally:
         ops._linear_choice = saved
 
