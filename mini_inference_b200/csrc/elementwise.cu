@@ -161,7 +161,7 @@ add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const WT*
     }
 }
 
-// Many rows: one WARP per row (shuffles only, no block barrier), 4 rows per block.  Every 16-byte piece of the row and
+// Very many rows: one WARP per row (shuffles only, no block barrier), 4 rows per block.  Every 16-byte piece of the row and
 // of the addition is requested before the first is used: a store to x between two loads of x would make the compiler
 // keep them in order, one round trip to memory each.  The summed row stays packed in registers for the second pass.
 template <typename T, typename WT, int VPT>
@@ -233,7 +233,9 @@ MI_EXPORT int mi_add_rmsnorm_ahead(void* x, const void* delta, const void* w, vo
     const bool vec = hidden % vw == 0 && hidden / vw <= NT * (dtype == MI_BF16 ? 4 : 8) &&
                      ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)delta % 16 == 0);
     const int nvec = hidden / vw;
-    const bool by_warp = vec && num_rows >= 64 && nvec <= 32 * 16;
+    // one warp per row only for long prompts: measured at width 2560, a 2,048-token step is 1-2 % faster with it, but at
+    // 64 rows (16 blocks on 148 SMs) it cost a decode step 7 %, and alone it is behind a block per row up to 1,024 rows
+    const bool by_warp = vec && num_rows >= 1024 && nvec <= 32 * 16;
     const int work = by_warp ? (num_rows + 3) / 4 : num_rows;
     const int blocks = work + l2_ahead_extra(ahead_ptr, ahead_bytes, work);
     const unsigned char* ahead = (const unsigned char*)ahead_ptr;

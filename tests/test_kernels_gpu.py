@@ -66,17 +66,20 @@ def test_add_rmsnorm(ops, dtype, hidden, w32):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden", [64, 2560, 4096, 5120, 1001])
 def test_add_rmsnorm_many_rows(ops, dtype, hidden):
-    """Row counts at which the one-warp-per-row kernel is used."""
+    """Row counts at which the one-warp-per-row kernel is used (from 1,024 rows), and just below."""
     g = torch.Generator().manual_seed(11)
-    x = (torch.randn(203, hidden, generator=g) * 2).to(dtype).to(DEV)
-    d = torch.randn(203, hidden, generator=g).to(dtype).to(DEV)
-    w = (torch.rand(hidden, generator=g) + 0.5).to(dtype).to(DEV)
     ref = TorchRefOps()
-    x1, x2 = x.clone(), x.clone()
-    close(ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6), dtype)
-    assert torch.equal(x1, x2)
-    rows = torch.arange(0, 203, 2, dtype=torch.int32, device=DEV)
-    close(ops.add_rmsnorm(x.clone(), None, w, 1e-6, rows), ref.add_rmsnorm(x.clone(), None, w, 1e-6, rows), dtype)
+    w = (torch.rand(hidden, generator=g) + 0.5).to(dtype).to(DEV)
+    for n in (203, 1027):
+        x = (torch.randn(n, hidden, generator=g) * 2).to(dtype).to(DEV)
+        d = torch.randn(n, hidden, generator=g).to(dtype).to(DEV)
+        x1, x2 = x.clone(), x.clone()
+        close(ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6), dtype)
+        assert torch.equal(x1, x2)
+        rows = torch.arange(0, n, 2, dtype=torch.int32, device=DEV)
+        close(ops.add_rmsnorm(x.clone(), None, w, 1e-6, rows), ref.add_rmsnorm(x.clone(), None, w, 1e-6, rows), dtype)
+    rows = torch.arange(0, 2 * 1100, 2, dtype=torch.int32, device=DEV) % 1027      # many selected rows of few
+    close(ops.add_rmsnorm(x.clone(), d, w, 1e-6, rows), ref.add_rmsnorm(x.clone(), d, w, 1e-6, rows), dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
