@@ -79,6 +79,10 @@ struct FusedQK {
 };
 
 constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per warp
+constexpr int DEC_BAR_BYTES = 256; // room for the rings' mbarriers (warps x DEC_STAGES x 8 bytes)
+constexpr int DEC_WARPS_ALONE = 8; // warps of a block that has its SM to itself (the grid is at most one block per SM):
+                                   // a warp works through its tiles one after the other, so with few blocks the time
+                                   // goes with the number of warps, not with the bytes
 
 // BULK = false: K/V go from the pages straight into registers (one block ahead).
 // BULK = true:  each warp keeps a ring of DEC_STAGES (K tile, V tile) pairs in shared memory, filled by TMA tile
@@ -87,8 +91,8 @@ constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per w
 //               swizzle spreads the 8 keys of a quarter-warp over the banks; the score product takes its 16-byte
 //               pieces in the order 2c + (j & 1) so that neighbouring lanes also differ in the column).  More bytes
 //               in flight per SM at no register cost.
-template <int D, bool BULK>
-__global__ void __launch_bounds__(DEC_WARPS * 32, BULK ? 2 : 3)
+template <int D, bool BULK, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS > DEC_WARPS ? 1 : BULK ? 2 : 3)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                        const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
@@ -97,10 +101,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
                        float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word,
                        const FusedQK fq, int cluster_merge) {
+    static_assert(WARPS * DEC_STAGES * 8 <= DEC_BAR_BYTES, "the mbarriers must fit in front of the fused-preamble scratch");
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
-    extern __shared__ float smem_raw[];  // [DEC_WARPS][16][D] outputs, then [DEC_WARPS][16] max and sum
+    extern __shared__ float smem_raw[];  // [WARPS][16][D] outputs, then [WARPS][16] max and sum
     float* smem = smem_raw;
     pdl_trigger();
     if (!BULK) pdl_wait();
@@ -120,8 +125,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     // same for all warps and live in shared memory ([k-step][lane] x 16 bytes) to keep registers
     // for the loads in flight.
     constexpr int TILE = 16 * D * 2;                                     // bytes of one K or V tile
-    constexpr int MERGE_BYTES = DEC_WARPS * 16 * (D + 2) * 4;
-    constexpr int RING_BYTES = BULK ? DEC_WARPS * DEC_STAGES * 2 * TILE : 0;
+    constexpr int MERGE_BYTES = WARPS * 16 * (D + 2) * 4;
+    constexpr int RING_BYTES = BULK ? WARPS * DEC_STAGES * 2 * TILE : 0;
     constexpr int FRONT = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;   // the merge scratch re-uses the ring
     constexpr int CLUSTER_OFF = (MERGE_BYTES + 1023) / 1024 * 256;               // (floats) this split's result, after the scratch
     unsigned char* smem_bytes = reinterpret_cast<unsigned char*>(smem);
@@ -133,7 +138,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bytes + FRONT + (D / 16) * 32 * 16);
     unsigned char* ring = smem_bytes + warp * (DEC_STAGES * 2 * TILE);
     // fused q/k preparation: the group's finished queries [16][D] and the new token's key and value
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_bytes + FRONT + (D / 16) * 32 * 16 + 128);
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_bytes + FRONT + (D / 16) * 32 * 16 + DEC_BAR_BYTES);
     __nv_bfloat16* knew = qs + 16 * D;
     __nv_bfloat16* vnew = knew + D;
     const int blk_new = (len - 1) / 16;
@@ -164,8 +169,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     int primed = 0;
     if (BULK) {
         __syncwarp();
-        for (; primed < DEC_STAGES && b0 + warp + primed * DEC_WARPS < min(b1, blk_hi - 1); ++primed)
-            issue(b0 + warp + primed * DEC_WARPS, primed);
+        for (; primed < DEC_STAGES && b0 + warp + primed * WARPS < min(b1, blk_hi - 1); ++primed)
+            issue(b0 + warp + primed * WARPS, primed);
         pdl_wait();
     }
     if (BULK && fq.qkv != nullptr) {
@@ -200,7 +205,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 o[e] = fq.inv_freq ? (second ? n * cs[e] + partner * sn[e] : n * cs[e] - partner * sn[e]) : n;
             }
         };
-        for (int r = warp; r < 16; r += DEC_WARPS) {
+        for (int r = warp; r < 16; r += WARPS) {
             float x[EPL], o[EPL];
             if (r < G) {
                 load_head(row + (size_t)(kvh * G + r) * D, x);
@@ -211,7 +216,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             }
             store_head(qs + r * D, o);
         }
-        if (writes_new && warp == DEC_WARPS - 1) {         // this block's range holds the new token: its key and value
+        if (writes_new && warp == WARPS - 1) {         // this block's range holds the new token: its key and value
             const int slot = fq.slots[tok];
             const size_t at = ((size_t)((slot / ps) * KV + kvh) * ps + (slot % ps)) * D;
             float x[EPL], o[EPL];
@@ -295,9 +300,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     int blk = b0 + warp;
     int nth = 0;
     if (BULK) {
-        for (int st = primed; st < DEC_STAGES && blk + st * DEC_WARPS < b1; ++st) issue(blk + st * DEC_WARPS, st);
+        for (int st = primed; st < DEC_STAGES && blk + st * WARPS < b1; ++st) issue(blk + st * WARPS, st);
     } else if (blk < b1) { load_k(blk); load_v(blk); }
-    for (; blk < b1; blk += DEC_WARPS, ++nth) {
+    for (; blk < b1; blk += WARPS, ++nth) {
         if (BULK) {
             const int st = nth % DEC_STAGES;
             if (!sm100::mbar_wait(bar0 + 8 * st, (nth / DEC_STAGES) & 1)) { if (lane == 0) atomicExch(error_word, 31); break; }
@@ -313,7 +318,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             frag_k_sw(tile);
             frag_v_sw(tile + TILE);
             __syncwarp();
-            if (blk + DEC_STAGES * DEC_WARPS < b1) issue(blk + DEC_STAGES * DEC_WARPS, st);
+            if (blk + DEC_STAGES * WARPS < b1) issue(blk + DEC_STAGES * WARPS, st);
         }
         // scores: 16 (heads) x 16 (keys) as two 8-key tiles
         float sc[2][4];
@@ -327,7 +332,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 mma_bf16_16816(sc[nt], qa1, kreg[nt][j].z, kreg[nt][j].w);
             }
         }
-        if (!BULK && blk + DEC_WARPS < b1) load_k(blk + DEC_WARPS);   // next block's keys fly during the rest
+        if (!BULK && blk + WARPS < b1) load_k(blk + WARPS);   // next block's keys fly during the rest
         // mask, online softmax (base 2)
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -377,7 +382,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 mma_bf16_16816(acc, pa, vb0, vb1);
             }
         }
-        if (!BULK && blk + DEC_WARPS < b1) load_v(blk + DEC_WARPS);
+        if (!BULK && blk + WARPS < b1) load_v(blk + WARPS);
     }
     if (BULK) __syncthreads();                    // every warp is done with its ring before the merge scratch overwrites it
 
@@ -385,8 +390,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     float* so = smem + (size_t)warp * 16 * D;
-    float* sm = smem + (size_t)DEC_WARPS * 16 * D;
-    float* sl = sm + DEC_WARPS * 16;
+    float* sm = smem + (size_t)WARPS * 16 * D;
+    float* sl = sm + WARPS * 16;
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         const int d0 = 64 * (t >> 3) + 8 * (2 * c) + (t & 7), d1 = d0 + 8;
@@ -398,14 +403,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         sm[warp * 16 + g + 8] = m1; sl[warp * 16 + g + 8] = l1;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+    for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
         const int row = idx / D, d = idx % D;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, sm[w * 16 + row]);
+        for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm[w * 16 + row]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float f = sm[w * 16 + row] == -INFINITY ? 0.f : exp2f(sm[w * 16 + row] - mx);
             num += f * smem[((size_t)w * 16 + row) * D + d];
             den += f * sl[w * 16 + row];
@@ -431,7 +436,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         cluster_sync();
         if (cluster_rank() == 0) {
             const float* cpart = smem + CLUSTER_OFF;
-            for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+            for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
                 const int row = idx / D, d = idx % D, h = kvh * G + row;
                 float l[8], v[8], mx = -INFINITY;
 #pragma unroll
@@ -464,7 +469,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+    for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
         const int row = idx / D, d = idx % D, h = kvh * G + row;
         const size_t base = ((size_t)blockIdx.x * H + h) * S;
         float mx = -INFINITY, num = 0.f, den = 0.f;
@@ -571,7 +576,7 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
 MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
     if ((D != 64 && D != 128) || splits < 2 || splits > 8) return 0;
     const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
-                        1024 + 128 + 18 * D * 2;
+                        1024 + DEC_BAR_BYTES + 18 * D * 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, splits); cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
@@ -581,11 +586,11 @@ MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
     int n = 0;
     cudaError_t e;
     if (D == 128) {
-        cudaFuncSetAttribute(attn_decode_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<128, true>, &cfg);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<128, true, DEC_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<128, true, DEC_WARPS>, &cfg);
     } else {
-        cudaFuncSetAttribute(attn_decode_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<64, true>, &cfg);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64, true, DEC_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<64, true, DEC_WARPS>, &cfg);
     }
     return e == cudaSuccess ? n : 0;
 }
@@ -622,21 +627,28 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
         if (rc) return rc;
         if ((rc = cache_map(v_cache, rows, D, &vmap))) return rc;
     }
-    const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (D + 2) * sizeof(float);
-    const size_t ring_bytes = bulk ? (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 : 0;
-    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
-                        (bulk ? 1024 + 128 + 18 * D * 2 : 0);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 1;
+    }
+    const bool alone = bulk && (long long)num_decode * KV * splits <= sms;      // at most one block per SM
+    const int warps = alone ? DEC_WARPS_ALONE : DEC_WARPS;
+    const size_t merge_bytes = (size_t)warps * 16 * (D + 2) * sizeof(float);
+    const size_t ring_bytes = bulk ? (size_t)warps * DEC_STAGES * 2 * 16 * D * 2 : 0;
+    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + warps * DEC_STAGES * 8 +
+                        (bulk ? 1024 + DEC_BAR_BYTES + 18 * D * 2 : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
     int use_cluster = (error_word != nullptr && cluster_merge && splits >= 2 && splits <= 8) ? 1 : 0;
-#define LAUNCH(DD, BB) do { \
+#define LAUNCH(DD, BB, WW) do { \
         static bool configured = false; \
         if (!configured && smem > 48 * 1024) { \
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
         cudaLaunchConfig_t cfg = {}; \
-        cfg.gridDim = grid; cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
+        cfg.gridDim = grid; cfg.blockDim = dim3(WW * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
         cudaLaunchAttribute attr[2]; \
         attr[0].id = cudaLaunchAttributeClusterDimension; \
         attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits; \
@@ -649,19 +661,19 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
             if (fit[splits] == 0) { \
                 cfg.attrs = attr; cfg.numAttrs = 1; \
                 int n = 0; \
-                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB>, &cfg) != cudaSuccess || n < 1) n = -1; \
+                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB, WW>, &cfg) != cudaSuccess || n < 1) n = -1; \
                 fit[splits] = n; \
             } \
             /* (with a margin: blocks of the kernels before and after share the SMs for a moment) */ \
             if (fit[splits] < 0 || (long long)num_decode * KV * 100 > (long long)fit[splits] * 92) use_cluster = 0; \
         } \
         cfg.attrs = use_cluster ? attr : attr + 1; cfg.numAttrs = use_cluster ? 2 : 1; \
-        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB>, kmap, vmap, \
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
             H, KV, ps, scale_log2, window, merge_counters, error_word, fq, use_cluster); } while (0)
-    if (D == 128) { if (bulk) LAUNCH(128, true); else LAUNCH(128, false); }
-    else { if (bulk) LAUNCH(64, true); else LAUNCH(64, false); }
+    if (D == 128) { if (alone) LAUNCH(128, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(128, true, DEC_WARPS); else LAUNCH(128, false, DEC_WARPS); }
+    else { if (alone) LAUNCH(64, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(64, true, DEC_WARPS); else LAUNCH(64, false, DEC_WARPS); }
 #undef LAUNCH
     return (int)cudaGetLastError();
 }
