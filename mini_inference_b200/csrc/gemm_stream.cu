@@ -79,6 +79,10 @@ template <> __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(floa
 __device__ __forceinline__ int owner_of(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
 
 template <int NT, typename OutT>
+// The register count of the 8-token instance matters beyond this kernel (tests/test_kernel_resources.py guards it): at 112
+// registers a decode step at Qwen3-4B sizes takes 3.05 ms, at 115 (an unrelated, never executed branch more in the
+// producer) 3.49 ms, while the kernel timed alone is equally fast either way.  Inside a step the blocks of the kernels
+// around it share the SMs with this one (programmatic dependent launch); past 112 registers a thread they no longer fit.
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    OutT* __restrict__ out, int ldo, int M, int N, int K, float* __restrict__ workspace, int max_contrib,
