@@ -83,6 +83,9 @@ template <int NT, typename OutT>
 // registers a decode step at Qwen3-4B sizes takes 3.05 ms, at 115 (an unrelated, never executed branch more in the
 // producer) 3.49 ms, while the kernel timed alone is equally fast either way.  Inside a step the blocks of the kernels
 // around it share the SMs with this one (programmatic dependent launch); past 112 registers a thread they no longer fit.
+// The arithmetic that matches: an SM's registers are four banks of 16,384, one per scheduler; the fullest bank holds 3 of
+// this block's 9 warps and must also take 5 of the 20 warps (32 registers each) of the residual-add + norm block that
+// follows: 3 * 32 * r + 5 * 32 * 32 <= 16,384 gives r <= 117, and registers are handed out in eights.
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    OutT* __restrict__ out, int ldo, int M, int N, int K, float* __restrict__ workspace, int max_contrib,
