@@ -13,6 +13,13 @@ Call order for a request: admit -> (ensure -> commit)* -> free.
   ensure(seq, n)  pages for positions < n exist in every group, all or nothing
                   (the reference's reserve() keeps a partial grab, kv_cache.py:216-224)
   commit(seq, n)  n tokens are now cached; pages a window has passed are given back
+
+Block tables live twice: a host array per group ([slots + 1, max pages], the truth) and a
+device copy of the same shape that the attention kernels read, a request's row being its
+state slot.  The reference rebuilds and copies a padded table every step
+(kv_cache.py:403-420); here every change of a host entry is noted, and a step sends only the
+entries that changed since the last one (take_table_updates): a decode step sends at most a
+new page and a released page per request, whatever the context length.
 """
 from __future__ import annotations
 
@@ -45,6 +52,8 @@ class _Group:
         self.pool: Optional[PagePool] = None
         self.storage = None                              # kv groups
         self.tables: Optional[np.ndarray] = None         # [slots + 1, max_pages] int32 (host)
+        self.device_table = None                         # the same on the device, kept current by update lists
+        self.dirty: dict = {}                            # flat index -> None, in the order the entries changed
 
 
 class CacheManager:
@@ -80,6 +89,7 @@ class CacheManager:
             g.pool = PagePool(num_pages)
             g.tables = np.zeros((max_seqs + 1, self.max_pages_per_seq), dtype=np.int32)
             if allocate:
+                g.device_table = torch.zeros((max_seqs + 1, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
                 n = g.need
                 g.storage = torch.zeros((len(g.steps), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                         dtype=dtype, device=self.device)
@@ -103,8 +113,23 @@ class CacheManager:
         el = torch.empty((), dtype=self.dtype).element_size()
         return sum(2 * len(g.steps) * g.need.num_kv_heads * g.need.head_dim * el for g in self.kv_groups)
 
+    def state_bytes_per_seq(self) -> int:
+        """Bytes of fixed-size state one live request occupies over all state groups."""
+        el = torch.empty((), dtype=self.dtype).element_size()
+        return sum(math.prod(g.need.shape) * (el if g.need.dtype == "compute" else 4) for g in self.state_groups)
+
     def pages_for(self, num_tokens: int) -> int:
         return math.ceil(num_tokens / self.page_size)
+
+    def peak_pages(self, g: "_Group", total_len: int, max_span: Optional[int]) -> int:
+        """Most pages of group g that a request of total_len tokens holds at one time when no step feeds it more
+        than max_span tokens (None: a step may feed all of them).  A windowed group keeps the pages that the
+        window of the next position reaches plus those of the span being written."""
+        full = self.pages_for(total_len)
+        W = g.need.window
+        if W is None or max_span is None:
+            return full
+        return min(full, self.pages_for(W + max_span) + 1)
 
     def _first_needed_page(self, g: _Group, num_cached: int) -> int:
         """First page index that holds a key some position >= num_cached may still read."""
@@ -117,25 +142,24 @@ class CacheManager:
     def free_pages(self) -> int:
         return min((g.pool.num_free for g in self.kv_groups), default=self.num_pages)
 
-    def can_admit(self, total_len: int) -> bool:
-        """engine/core/kv_cache.py:192-197: pages for the whole request plus the watermark
-        must be free (in every group), and a state slot."""
+    def can_admit(self, total_len: int, max_span: Optional[int] = None) -> bool:
+        """engine/core/kv_cache.py:192-197: the pages the request will hold plus the watermark must be free, in
+        every group (a windowed group is charged what it holds at its peak, see peak_pages), and a state slot."""
         if self.slots.num_free == 0 or total_len > self.max_pages_per_seq * self.page_size:
             return False
-        return self.pages_for(total_len) + self.watermark_pages <= self.free_pages()
+        return all(self.peak_pages(g, total_len, max_span) + self.watermark_pages <= g.pool.num_free
+                   for g in self.kv_groups)
 
-    def admit(self, seq_id, total_len: Optional[int] = None) -> Optional[SeqCache]:
+    def admit(self, seq_id, total_len: Optional[int] = None, max_span: Optional[int] = None) -> Optional[SeqCache]:
         if seq_id in self.seqs:
             raise RuntimeError(f"request {seq_id!r} is already admitted")
-        if total_len is not None and not self.can_admit(total_len):
+        if total_len is not None and not self.can_admit(total_len, max_span):
             return None
         slot = self.slots.claim()
         if slot is None:
             return None
         seq = SeqCache(seq_id, slot, len(self.kv_groups))
         self.seqs[seq_id] = seq
-        for g in self.kv_groups:
-            g.tables[slot, :] = 0
         for g in self.state_groups:
             if g.storage is not None:
                 g.storage[slot].zero_()
@@ -151,8 +175,10 @@ class CacheManager:
                 return False
         for gi, g in enumerate(self.kv_groups):
             row = g.tables[seq.slot]
+            base = seq.slot * self.max_pages_per_seq
             for idx in range(seq.num_pages[gi], want):
                 row[idx] = g.pool.take()
+                g.dirty[base + idx] = None
             seq.num_pages[gi] = max(seq.num_pages[gi], want)
         return True
 
@@ -161,9 +187,11 @@ class CacheManager:
         for gi, g in enumerate(self.kv_groups):
             keep_from = min(self._first_needed_page(g, num_tokens), seq.num_pages[gi])
             row = g.tables[seq.slot]
+            base = seq.slot * self.max_pages_per_seq
             for idx in range(seq.first_live[gi], keep_from):
                 g.pool.give(int(row[idx]))
                 row[idx] = PagePool.NULL_PAGE
+                g.dirty[base + idx] = None
             seq.first_live[gi] = max(seq.first_live[gi], keep_from)
 
     def free(self, seq: SeqCache) -> None:
@@ -174,9 +202,11 @@ class CacheManager:
         seq.alive = False
         for gi, g in enumerate(self.kv_groups):
             row = g.tables[seq.slot]
+            base = seq.slot * self.max_pages_per_seq
             for idx in range(seq.first_live[gi], seq.num_pages[gi]):
                 g.pool.give(int(row[idx]))
-            row[:] = 0
+                row[idx] = PagePool.NULL_PAGE
+                g.dirty[base + idx] = None
         self.slots.release(seq.slot)
         del self.seqs[seq.seq_id]
 
@@ -191,6 +221,25 @@ class CacheManager:
     def table_rows(self, gi: int, seqs, num_cols: int) -> np.ndarray:
         return self.kv_groups[gi].tables[[s.slot for s in seqs], :num_cols]
 
+    def pending_table_updates(self, gi: int) -> int:
+        return len(self.kv_groups[gi].dirty)
+
+    def take_table_updates(self, gi: int, limit: Optional[int] = None):
+        """(flat indices, values) of up to `limit` block-table entries of group gi whose host value changed since they
+        were last taken, oldest change first; the caller writes them into the device table before the kernels of
+        its step run.  An entry changed twice is sent once, with its current value."""
+        g = self.kv_groups[gi]
+        n = len(g.dirty) if limit is None else min(limit, len(g.dirty))
+        if n == len(g.dirty):
+            idx = np.fromiter(g.dirty, dtype=np.int64, count=n)
+            g.dirty = {}
+        else:
+            keys = list(g.dirty)[:n]
+            for k in keys:
+                del g.dirty[k]
+            idx = np.asarray(keys, dtype=np.int64)
+        return idx.astype(np.int32), g.tables.reshape(-1)[idx]
+
     # ---------------------------------------------------------------- checks and numbers
     def check_invariants(self) -> None:
         """No page lost, none held twice, free list and tables disjoint (used by the tests)."""
@@ -203,6 +252,14 @@ class CacheManager:
                 assert not row[:seq.first_live[gi]].any() and not row[seq.num_pages[gi]:].any(), \
                     f"group {gi}: table entries outside the live range are not null"
                 held += live
+            for slot in range(g.tables.shape[0]):
+                if slot not in {s.slot for s in self.seqs.values()}:
+                    assert not g.tables[slot].any(), f"group {gi}: row {slot} belongs to nobody and is not null"
+            if g.device_table is not None:
+                mirror = g.device_table.cpu().numpy().reshape(-1).copy()
+                for k in g.dirty:
+                    mirror[k] = g.tables.reshape(-1)[k]
+                assert (mirror == g.tables.reshape(-1)).all(), f"group {gi}: device table differs beyond the noted changes"
             free = list(g.pool.free)
             assert len(set(held)) == len(held), f"group {gi}: a page is held twice"
             assert len(set(free)) == len(free), f"group {gi}: a page is in the free list twice"

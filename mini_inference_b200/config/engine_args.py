@@ -39,6 +39,7 @@ class EngineArgs:
     temperature: float = 0.7                                                                        # config.py:122
     seed: int = 0
     device: str = "cuda:0"
+    nvtx: bool = field(default_factory=lambda: _env("NVTX", bool, False))                           # config.py:155
 
     def __post_init__(self):
         self.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(self.dtype, self.dtype)

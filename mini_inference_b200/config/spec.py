@@ -38,16 +38,22 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (block) of a mixer, a feed-forward, norms and a position
-    encoding.  weight_names maps each part's own tensor names ("mixer.q_proj",
-    "feed_forward.down_proj", "norm1.weight", ...) to the checkpoint's names, so that no part
-    knows a checkpoint's naming."""
+    """One layer: an arrangement (block) and the parts it arranges, by ROLE.  Which roles exist
+    is the block's business: the pre-norm block takes "mixer", "feed_forward", "norm1", "norm2"
+    and "position"; a block with one shared norm, or with four, names its own.  weight_names
+    maps each part's tensor names, prefixed by its role ("mixer.q_proj", "norm1.weight", ...),
+    to the checkpoint's names, so that no part knows a checkpoint's naming."""
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    norm: PartSpec
-    position: PartSpec
+    parts: Tuple[Tuple[str, PartSpec], ...]
     weight_names: Tuple[Tuple[str, str], ...]
+
+    @staticmethod
+    def of(block: str, weight_names, **parts: PartSpec) -> "LayerSpec":
+        names = weight_names.items() if isinstance(weight_names, Mapping) else weight_names
+        return LayerSpec(block, tuple(parts.items()), tuple(sorted(names)))
+
+    def part(self, role: str) -> PartSpec:
+        return dict(self.parts)[role]
 
     def checkpoint_name(self, part_tensor: str) -> str:
         return dict(self.weight_names)[part_tensor]

@@ -63,21 +63,6 @@ __device__ __forceinline__ float ld_cluster(const float* local, uint32_t rank) {
     return v;
 }
 
-// Optional work of the kernel before this one, done in this kernel's preamble when every row of the step is a decoded
-// token: per-head RMSNorm of q and k, rotation, and the write of the new token's k and v into the pages
-// (csrc/qk_rope_cache.cu, same arithmetic and rounding).  qkv == nullptr: q arrives finished and the cache is complete.
-struct FusedQK {
-    const __nv_bfloat16* qkv;           // [T, (H + 2 KV) D] raw projections
-    const __nv_bfloat16* q_w;           // [D] or null (no norm)
-    const __nv_bfloat16* k_w;
-    const float* inv_freq;              // [D / 2] or null (no rotation)
-    const int* positions;               // [T]
-    const int* slots;                   // [T] cache position of each token: page * page_size + offset
-    __nv_bfloat16* k_out;               // the caches to write the new token into; null: the layer reads another's cache
-    __nv_bfloat16* v_out;
-    float eps;
-};
-
 constexpr int DEC_STAGES = 3;      // BULK: 16-key K and V tiles in flight per warp
 constexpr int DEC_BAR_BYTES = 256; // room for the rings' mbarriers (warps x DEC_STAGES x 8 bytes)
 constexpr int DEC_WARPS_ALONE = 8; // warps of a block that has its SM to itself (the grid is at most one block per SM):
@@ -98,10 +83,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ o_part, float* __restrict__ lse_part, const int* __restrict__ decode_segs,
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
-                       const int* __restrict__ block_table, int table_stride, int H, int KV, int ps,
-                       float scale_log2, int window, int* __restrict__ merge_counters, int* __restrict__ error_word,
-                       const FusedQK fq, int cluster_merge) {
-    static_assert(WARPS * DEC_STAGES * 8 <= DEC_BAR_BYTES, "the mbarriers must fit in front of the fused-preamble scratch");
+                       const int* __restrict__ block_table, const int* __restrict__ table_rows, int table_stride,
+                       int H, int KV, int ps, float scale_log2, int window, int* __restrict__ merge_counters,
+                       int* __restrict__ error_word, int cluster_merge) {
+    static_assert(WARPS * DEC_STAGES * 8 <= DEC_BAR_BYTES, "the mbarriers must fit in their reserved bytes");
     constexpr int KS = D / 16;          // k-steps of the score product
     constexpr int NT = D / 8;           // output tiles of 8 columns
     constexpr int HALVES = D / 64;      // 64-column halves of a value row
@@ -119,7 +104,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     const int blk_lo = lo / 16, blk_hi = (len + 15) / 16;
     const int per = (blk_hi - blk_lo + S - 1) / S;
     const int b0 = blk_lo + s * per, b1 = min(b0 + per, blk_hi);
-    const int* table_row = block_table + (size_t)seg * table_stride;
+    // an entry's pages: row `seg` of the table, or row table_rows[seg] of a table that holds a row per live request
+    const int* table_row = block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride;
 
     // query fragments, permuted: the 16 bytes at d = 32 j + 8 c of rows g and g + 8.  They are the
     // same for all warps and live in shared memory ([k-step][lane] x 16 bytes) to keep registers
@@ -137,12 +123,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     uint4* q_frag = reinterpret_cast<uint4*>(smem_bytes + FRONT);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_bytes + FRONT + (D / 16) * 32 * 16);
     unsigned char* ring = smem_bytes + warp * (DEC_STAGES * 2 * TILE);
-    // fused q/k preparation: the group's finished queries [16][D] and the new token's key and value
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_bytes + FRONT + (D / 16) * 32 * 16 + DEC_BAR_BYTES);
-    __nv_bfloat16* knew = qs + 16 * D;
-    __nv_bfloat16* vnew = knew + D;
-    const int blk_new = (len - 1) / 16;
-    const bool writes_new = BULK && fq.qkv != nullptr && fq.k_out != nullptr && blk_new >= b0 && blk_new < b1;
     const uint32_t bar0 = sm100::smem_u32(bars + warp * DEC_STAGES);
     if (BULK && lane == 0) {
         for (int st = 0; st < DEC_STAGES; ++st) sm100::mbar_init(bar0 + 8 * st, 1);
@@ -173,66 +153,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             issue(b0 + warp + primed * WARPS, primed);
         pdl_wait();
     }
-    if (BULK && fq.qkv != nullptr) {
-        constexpr int EPL = D / 32;                        // elements per lane: one head spans the warp
-        const int heads = H + 2 * KV, d0 = lane * EPL;
-        const bool second = d0 >= D / 2;
-        const int i0 = second ? d0 - D / 2 : d0;
-        const __nv_bfloat16* row = fq.qkv + (size_t)tok * heads * D;
-        float cs[EPL], sn[EPL];
-        if (fq.inv_freq) {
-            const float pos = (float)fq.positions[tok];
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) sincosf(pos * fq.inv_freq[i0 + e], &sn[e], &cs[e]);
-        }
-        auto load_head = [&](const __nv_bfloat16* src, float* x) {
-#pragma unroll
-            for (int e = 0; e < EPL; e += 2) load2(src + d0 + e, x[e], x[e + 1]);
-        };
-        auto store_head = [&](__nv_bfloat16* dst, const float* v) {
-#pragma unroll
-            for (int e = 0; e < EPL; e += 2) store2(dst + d0 + e, v[e], v[e + 1]);
-        };
-        auto norm_rope = [&](const float* x, const __nv_bfloat16* w, float* o) {
-            float ss = 0.f;
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) ss += x[e] * x[e];
-            const float rstd = rsqrtf(warp_sum(ss) / (float)D + fq.eps);
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-                const float n = w ? round_to<__nv_bfloat16>(round_to<__nv_bfloat16>(x[e] * rstd) * __bfloat162float(w[d0 + e])) : x[e];
-                const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
-                o[e] = fq.inv_freq ? (second ? n * cs[e] + partner * sn[e] : n * cs[e] - partner * sn[e]) : n;
-            }
-        };
-        for (int r = warp; r < 16; r += WARPS) {
-            float x[EPL], o[EPL];
-            if (r < G) {
-                load_head(row + (size_t)(kvh * G + r) * D, x);
-                norm_rope(x, fq.q_w, o);
-            } else {
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) o[e] = 0.f;
-            }
-            store_head(qs + r * D, o);
-        }
-        if (writes_new && warp == WARPS - 1) {         // this block's range holds the new token: its key and value
-            const int slot = fq.slots[tok];
-            const size_t at = ((size_t)((slot / ps) * KV + kvh) * ps + (slot % ps)) * D;
-            float x[EPL], o[EPL];
-            load_head(row + (size_t)(H + kvh) * D, x);
-            norm_rope(x, fq.k_w, o);
-            store_head(knew, o);
-            store_head(fq.k_out + at, o);
-            load_head(row + (size_t)(H + KV + kvh) * D, x);
-            store_head(vnew, x);
-            store_head(fq.v_out + at, x);
-        }
-        __syncthreads();
-    }
     if (warp == 0) {
-        const bool prepared = BULK && fq.qkv != nullptr;
-        const __nv_bfloat16* qrow = prepared ? qs : q + (size_t)tok * q_stride + (size_t)kvh * G * D;
+        const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * D;
 #pragma unroll
         for (int j = 0; j < KS / 2; ++j) {
             uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
@@ -307,14 +229,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             const int st = nth % DEC_STAGES;
             if (!sm100::mbar_wait(bar0 + 8 * st, (nth / DEC_STAGES) & 1)) { if (lane == 0) atomicExch(error_word, 31); break; }
             unsigned char* tile = ring + st * 2 * TILE;
-            if (writes_new && blk == blk_new) {
-                // the tile came from the pages while this block was writing the new token there: put its row in place
-                const int r = (len - 1) % 16, piece = lane & 15;
-                if (piece < D / 8)
-                    *reinterpret_cast<uint4*>(tile + (lane < 16 ? 0 : TILE) + (piece >> 3) * 2048 + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) =
-                        *reinterpret_cast<const uint4*>((lane < 16 ? knew : vnew) + piece * 8);
-                __syncwarp();
-            }
             frag_k_sw(tile);
             frag_v_sw(tile + TILE);
             __syncwarp();
@@ -511,13 +425,12 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                       int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream);
 
-MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                    float* o_part, float* lse_part, const int* decode_segs, int num_decode,
-                                    const int* seg_q_start, const int* seg_kv_len, const int* block_table,
-                                    int table_stride, int H, int KV, int D, int ps, int splits, float scale,
-                                    int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
-                                    const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
-                                    const int* slots, int write_cache, float eps, int cluster_merge, cudaStream_t stream);
+MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                      const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                      float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                      int cluster_merge, cudaStream_t stream);
 
 MI_EXPORT int mi_attn_decode_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                  float* o_part, float* lse_part, const int* decode_segs, int num_decode,
@@ -567,16 +480,16 @@ MI_EXPORT int mi_attn_decode_mma_bulk(const void* q, int q_stride, const void* k
                                       const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                       int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                       int window, int* merge_counters, int* error_word, int cache_pages, cudaStream_t stream) {
-    return mi_attn_decode_mma_qk(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode, seg_q_start,
-                                 seg_kv_len, block_table, table_stride, H, KV, D, ps, splits, scale, window, merge_counters,
-                                 error_word, cache_pages, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0.f, 0, stream);
+    return mi_attn_decode_mma_rows(q, q_stride, k_cache, v_cache, out, o_part, lse_part, decode_segs, num_decode, seg_q_start,
+                                   seg_kv_len, block_table, nullptr, table_stride, H, KV, D, ps, splits, scale, window,
+                                   merge_counters, error_word, cache_pages, 0, stream);
 }
 
 // How many clusters of `splits` blocks of the staged kernel the GPU holds at once (0: unknown or none).
 MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
     if ((D != 64 && D != 128) || splits < 2 || splits > 8) return 0;
     const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2 + (size_t)(D / 16) * 32 * 16 + DEC_WARPS * DEC_STAGES * 8 +
-                        1024 + DEC_BAR_BYTES + 18 * D * 2;
+                        1024 + DEC_BAR_BYTES;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, splits); cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
@@ -595,27 +508,17 @@ MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
     return e == cudaSuccess ? n : 0;
 }
 
-// The staged variant with the work of mi_qk_norm_rope_cache done in its preamble, for steps whose rows are all decoded
-// tokens: qkv [num rows, (H + 2 KV) D] raw projections (q is ignored), q_w / k_w bfloat16 [D] or null, inv_freq float32
-// [D / 2] or null, positions and slots per row; write_cache = 0 when the layer reads another layer's cache (k, v unused).
-// qkv == null: exactly mi_attn_decode_mma_bulk.  cluster_merge != 0: with 2..8 splits the splits of a (request, kv head) are
-// launched as one thread-block cluster and merged through distributed shared memory (o_part, lse_part, merge_counters unused).
-MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                    float* o_part, float* lse_part, const int* decode_segs, int num_decode,
-                                    const int* seg_q_start, const int* seg_kv_len, const int* block_table,
-                                    int table_stride, int H, int KV, int D, int ps, int splits, float scale,
-                                    int window, int* merge_counters, int* error_word, int cache_pages, const void* qkv,
-                                    const void* q_w, const void* k_w, const float* inv_freq, const int* positions,
-                                    const int* slots, int write_cache, float eps, int cluster_merge, cudaStream_t stream) {
+// The general entry point.  table_rows != null: block_table holds a row per live request ([rows, table_stride], kept on
+// the device) and entry i reads row table_rows[i]; null: entry i reads row i.  cluster_merge != 0: with 2..8 splits the
+// splits of a (request, kv head) are launched as one thread-block cluster and merged through distributed shared memory
+// (o_part, lse_part, merge_counters unused).
+MI_EXPORT int mi_attn_decode_mma_rows(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                      const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                      float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                      int cluster_merge, cudaStream_t stream) {
     if (num_decode == 0) return 0;
-    if (qkv != nullptr && (error_word == nullptr || ((uintptr_t)qkv % 16))) return -2;
-    FusedQK fq = {};
-    if (qkv != nullptr) {
-        fq.qkv = (const __nv_bfloat16*)qkv; fq.q_w = (const __nv_bfloat16*)q_w; fq.k_w = (const __nv_bfloat16*)k_w;
-        fq.inv_freq = inv_freq; fq.positions = positions; fq.slots = slots; fq.eps = eps;
-        fq.k_out = write_cache ? (__nv_bfloat16*)k_cache : nullptr;
-        fq.v_out = write_cache ? (__nv_bfloat16*)v_cache : nullptr;
-    }
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
     const bool bulk = error_word != nullptr;
@@ -637,7 +540,7 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
     const size_t merge_bytes = (size_t)warps * 16 * (D + 2) * sizeof(float);
     const size_t ring_bytes = bulk ? (size_t)warps * DEC_STAGES * 2 * 16 * D * 2 : 0;
     const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + (size_t)(D / 16) * 32 * 16 + warps * DEC_STAGES * 8 +
-                        (bulk ? 1024 + DEC_BAR_BYTES + 18 * D * 2 : 0);
+                        (bulk ? 1024 + DEC_BAR_BYTES : 0);
     const float scale_log2 = scale * 1.4426950408889634f;
     int use_cluster = (error_word != nullptr && cluster_merge && splits >= 2 && splits <= 8) ? 1 : 0;
 #define LAUNCH(DD, BB, WW) do { \
@@ -670,8 +573,8 @@ MI_EXPORT int mi_attn_decode_mma_qk(const void* q, int q_stride, const void* k_c
         cfg.attrs = use_cluster ? attr : attr + 1; cfg.numAttrs = use_cluster ? 2 : 1; \
         return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-            (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_stride, \
-            H, KV, ps, scale_log2, window, merge_counters, error_word, fq, use_cluster); } while (0)
+            (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, \
+            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster); } while (0)
     if (D == 128) { if (alone) LAUNCH(128, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(128, true, DEC_WARPS); else LAUNCH(128, false, DEC_WARPS); }
     else { if (alone) LAUNCH(64, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(64, true, DEC_WARPS); else LAUNCH(64, false, DEC_WARPS); }
 #undef LAUNCH

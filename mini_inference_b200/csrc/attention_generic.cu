@@ -72,14 +72,14 @@ __global__ void attn_prefill_generic_kernel(const T* __restrict__ q, int q_strid
                                             const T* __restrict__ v_cache, T* __restrict__ out,
                                             const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
                                             const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
-                                            int table_stride, int H, int KV, int D, int ps, int tile_rows,
+                                            const int* __restrict__ table_rows, int table_stride, int H, int KV, int D, int ps, int tile_rows,
                                             float scale, int window) {
     __shared__ float q_s[WARPS][MAX_D];
     const int seg = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
     const int h = blockIdx.y, kvh = h / (H / KV);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
-    const int* table_row = block_table + (size_t)seg * table_stride;
+    const int* table_row = block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride;
     const int r_end = min(r0 + tile_rows, n);
     for (int r = r0 + warp; r < r_end; r += WARPS) {
         const int tok = qs + r, p = pos0 + r;
@@ -109,7 +109,7 @@ __global__ void attn_decode_split_kernel(const T* __restrict__ q, int q_stride, 
                                          float* __restrict__ o_part, float* __restrict__ lse_part,
                                          const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start,
                                          const int* __restrict__ seg_kv_len, const int* __restrict__ block_table,
-                                         int table_stride, int H, int KV, int D, int ps, float scale, int window) {
+                                         const int* __restrict__ table_rows, int table_stride, int H, int KV, int D, int ps, float scale, int window) {
     __shared__ float q_s[WARPS][MAX_D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * WARPS + warp;
@@ -129,7 +129,7 @@ __global__ void attn_decode_split_kernel(const T* __restrict__ q, int q_stride, 
 #pragma unroll
     for (int k = 0; k < MAX_D / 32; ++k) acc[k] = 0.f;
     if (lo < hi)
-        attend_range<T>(q_s[warp], k_cache, v_cache, block_table + (size_t)seg * table_stride, kvh, KV, D, ps,
+        attend_range<T>(q_s[warp], k_cache, v_cache, block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride, kvh, KV, D, ps,
                         lo, hi, m, l, acc);
     const float inv = l > 0.f ? 1.f / l : 0.f;                  // empty piece: output 0, lse -inf
     if (S == 1) {
@@ -168,32 +168,32 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ o_part, const
 
 MI_EXPORT int mi_attn_prefill_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                       const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
-                                      const int* block_table, int table_stride, int H, int KV, int D, int ps,
-                                      int tile_rows, float scale, int window, int dtype, cudaStream_t stream) {
+                                      const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D,
+                                      int ps, int tile_rows, float scale, int window, int dtype, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if (D > MAX_D || D % 8 || (dtype == MI_F32 && D % 4)) return -2;
     dim3 grid(num_tiles, H);
     if (dtype == MI_BF16)
         attn_prefill_generic_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_stride, H, KV, D, ps, tile_rows, scale, window);
+            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, D, ps, tile_rows, scale, window);
     else
         attn_prefill_generic_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, (float*)out, tiles, seg_q_start,
-            seg_pos0, block_table, table_stride, H, KV, D, ps, tile_rows, scale, window);
+            seg_pos0, block_table, table_rows, table_stride, H, KV, D, ps, tile_rows, scale, window);
     return (int)cudaGetLastError();
 }
 
 MI_EXPORT int mi_attn_decode_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                      float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                      const int* seg_q_start, const int* seg_kv_len, const int* block_table,
-                                     int table_stride, int H, int KV, int D, int ps, int splits, float scale,
+                                     const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits, float scale,
                                      int window, int dtype, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if (D > MAX_D || D % 8) return -2;
     dim3 grid(num_decode, (H + WARPS - 1) / WARPS, splits);
 #define ARGS(T) (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, (T*)out, o_part, lse_part, decode_segs, \
-        seg_q_start, seg_kv_len, block_table, table_stride, H, KV, D, ps, scale, window
+        seg_q_start, seg_kv_len, block_table, table_rows, table_stride, H, KV, D, ps, scale, window
     if (dtype == MI_BF16) attn_decode_split_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(ARGS(__nv_bfloat16));
     else attn_decode_split_kernel<float><<<grid, WARPS * 32, 0, stream>>>(ARGS(float));
 #undef ARGS

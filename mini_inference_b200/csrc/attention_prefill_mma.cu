@@ -55,8 +55,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
-                        const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_stride,
-                        int H, int KV, int ps, float scale_log2, int window) {
+                        const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                        const int* __restrict__ table_rows, int table_stride, int H, int KV, int ps, float scale_log2, int window) {
     constexpr int CH = D / 8;               // 16-byte chunks per row
     constexpr int KS = D / 16;              // k-steps of Q K^T
     constexpr int DT = D / 8;               // 8-column output tiles
@@ -74,7 +74,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int h = blockIdx.x, kvh = h / (H / KV);
     const int qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs, pos0 = seg_pos0[seg];
     const int rows = min(BQ, n - r0);
-    const int* table_row = block_table + (size_t)seg * table_stride;
+    const int* table_row = block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride;
     const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
     const int kt_lo = window > 0 ? max(0, p_first - window + 1) / BK : 0;
     const int kt_hi = p_last / BK;                                          // inclusive
@@ -213,8 +213,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 
 MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                   const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
-                                  const int* block_table, int table_stride, int H, int KV, int D, int ps, int tile_rows,
-                                  float scale, int window, cudaStream_t stream) {
+                                  const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                                  int tile_rows, float scale, int window, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
@@ -229,7 +229,7 @@ MI_EXPORT int mi_attn_prefill_mma(const void* q, int q_stride, const void* k_cac
         } \
         attn_prefill_mma_kernel<DD><<<grid, PF_WARPS * 32, smem, stream>>>( \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_stride, H, KV, ps, scale_log2, window); \
+            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window); \
     } while (0)
     if (D == 128) LAUNCH(128, 0); else LAUNCH(64, 1);
 #undef LAUNCH

@@ -58,8 +58,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                        const __grid_constant__ CUtensorMap vmap, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
-                       const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_stride,
-                       int H, int KV, int ps, float scale_log2, int window, int* __restrict__ error_word) {
+                       const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                       const int* __restrict__ table_rows, int table_stride, int H, int KV, int ps, float scale_log2, int window, int* __restrict__ error_word) {
     constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a head
     constexpr int Q_BYTES = BQ * D * 2, KV_BYTES = BKV * D * 2;
     constexpr int TMEM_COLS = 256;                       // S0: 64, S1: 64 (P overwrites the first 32 columns of its S), O: D
@@ -114,7 +114,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             for (int hb = 0; hb < HALVES; ++hb)
                 tma_load_2d(sQ + hb * (BQ * 128), &qmap, h * D + hb * 64, qs + r0, q_full);
         }
-        const int* table_row = block_table + (size_t)seg * table_stride;
+        const int* table_row = block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride;
         const int pages_per_tile = BKV / ps;
         const int ops_per_tile = pages_per_tile * HALVES;
         const uint32_t full = is_v ? v_full : k_full, empty = is_v ? v_empty : k_empty, dst0 = is_v ? sV : sK;
@@ -322,8 +322,8 @@ bool cache_map(const void* cache, long long rows, int D, int ps, CUtensorMap* ou
 // tiles: (entry, first row) of 128-row tiles.  cache_rows = pages (with the null page) * KV * page_size.
 MI_EXPORT int mi_attn_prefill_tc(const void* q, int q_stride, int num_tokens, const void* k_cache, const void* v_cache,
                                  long long cache_rows, void* out, const int* tiles, int num_tiles, const int* seg_q_start,
-                                 const int* seg_pos0, const int* block_table, int table_stride, int H, int KV, int D,
-                                 int ps, int tile_rows, float scale, int window, int* error_word, cudaStream_t stream) {
+                                 const int* seg_pos0, const int* block_table, const int* table_rows, int table_stride, int H,
+                                 int KV, int D, int ps, int tile_rows, float scale, int window, int* error_word, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8 || ps % 8 || BKV % ps || ((uintptr_t)q % 16)) return -2;
     CUtensorMap qmap, kmap, vmap;
@@ -340,7 +340,7 @@ MI_EXPORT int mi_attn_prefill_tc(const void* q, int q_stride, int num_tokens, co
             configured = true; \
         } \
         return (int)launch_pdl(attn_prefill_tc_kernel<DD>, grid, dim3(ATT_THREADS), smem, stream, qmap, kmap, vmap, \
-                               (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_stride, H, KV, ps, \
+                               (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, \
                                scale_log2, window, error_word); \
     } while (0)
     if (D == 128) LAUNCH(128, 0);

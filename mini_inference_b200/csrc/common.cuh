@@ -107,11 +107,24 @@ __device__ __forceinline__ void l2_prefetch_share(const unsigned char* base, lon
     }
 }
 
-// how many request-only blocks to add to a kernel that keeps `busy` blocks for itself
+// streaming multiprocessors of the current device (asked once)
+inline int device_sms() {
+    static const int n = [] {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+            sms = 1;
+        return sms;
+    }();
+    return n;
+}
+
+// how many request-only blocks to add to a kernel that keeps `busy` blocks for itself: the SMs it leaves idle, less a
+// margin of 8 for the blocks of the kernel that follows (at least 8 in any case)
 inline int l2_prefetch_blocks(long long bytes, int busy) {
     const long long pieces = (bytes + L2_AHEAD_PIECE - 1) / L2_AHEAD_PIECE;
     long long blocks = (pieces + 127) / 128;
-    const long long room = busy < 132 ? 140 - busy : 8;
+    const int sms = device_sms();
+    const long long room = busy < sms - 16 ? sms - 8 - busy : 8;
     if (blocks > room) blocks = room;
     return blocks < 1 ? 1 : (int)blocks;
 }

@@ -37,6 +37,25 @@ MI_EXPORT int mi_embedding(const int* ids, const void* table, void* out, int T_,
     return (int)launch_pdl(embedding_kernel<float>, dim3(T_), dim3(128), 0, stream, ids, (const float*)table, (float*)out, hidden, vocab);
 }
 
+// ------------------------------------------------------------------ block-table changes
+// table[idx[i]] = val[i] for the entries of the device block tables that changed on the host since the last step
+// (cache manager).  Launched plainly and without an early launch_dependents: every kernel of the step, also one whose
+// preamble reads the table before its own griddepcontrol.wait, starts after this one has ended.  Padding entries
+// write 0 at index 0 (the null row).  Indices outside the table are skipped.
+__global__ void scatter_i32_kernel(int* __restrict__ table, const int* __restrict__ idx, const int* __restrict__ val,
+                                   int n, long long table_size) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int at = idx[i];
+    if (at >= 0 && at < table_size) table[at] = val[i];
+}
+
+MI_EXPORT int mi_scatter_i32(int* table, const int* idx, const int* val, int n, long long table_size, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, idx, val, n, table_size);
+    return (int)cudaGetLastError();
+}
+
 // ------------------------------------------------------------------ (x += delta); y = rmsnorm(x) * w
 // One block per output row.  rows == nullptr: row r of x is updated in place with delta and
 // normalised.  rows != nullptr: output row r is the norm of x[rows[r]] (+ delta[rows[r]]),
@@ -299,7 +318,8 @@ MI_EXPORT int mi_swiglu(const void* gate_up, void* out, int rows, int inter, int
     const int vw = dtype == MI_BF16 ? 8 : 4;
     const bool vec = inter % vw == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
     const size_t work = vec ? n / vw : n;
-    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+    const int cap = device_sms() * 16;
+    const int blocks = (int)((work + 255) / 256 < cap ? (work + 255) / 256 : cap);
 #define LAUNCH(T) do { \
         if (vec) return (int)launch_pdl(swiglu_vec_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, rows, inter); \
         return (int)launch_pdl(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, rows, inter); \

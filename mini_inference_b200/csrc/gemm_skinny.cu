@@ -146,7 +146,7 @@ int launch(const void* X, int ldx, const void* W, void* out, int ldo, int M, int
 
 template <typename OutT>
 int dispatch(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K, cudaStream_t stream) {
-    const bool wide = (N + 31) / 32 >= 2 * 148;          // enough 32-row blocks to fill the GPU twice
+    const bool wide = (N + 31) / 32 >= 2 * device_sms();          // enough 32-row blocks to fill the GPU twice
     if (M <= 8) return wide ? launch<1, 2, 4, OutT>(X, ldx, W, out, ldo, M, N, K, stream)
                             : launch<1, 1, 4, OutT>(X, ldx, W, out, ldo, M, N, K, stream);
     if (M <= 16) return wide ? launch<2, 2, 4, OutT>(X, ldx, W, out, ldo, M, N, K, stream)

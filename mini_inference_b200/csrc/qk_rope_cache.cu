@@ -300,7 +300,8 @@ MI_EXPORT int mi_qk_norm_rope_cache(void* qkv, const void* q_w, const void* k_w,
     if (T_ == 0) return 0;
     if (D % 4 || D / 2 > MAX_HALF) return -2;
     const long long items = (long long)T_ * (H + 2 * KV);
-    const int blocks = (int)((items + 7) / 8 < 148 * 8 ? (items + 7) / 8 : 148 * 8);
+    const int cap = device_sms() * 8;
+    const int blocks = (int)((items + 7) / 8 < cap ? (items + 7) / 8 : cap);
 #define VEC(T, WT, L) return (int)launch_pdl(qk_norm_rope_cache_vec_kernel<T, WT, L>, dim3(T_, (H + 2 * KV + 256 / L - 1) / (256 / L)), dim3(256), 0, \
             stream, (T*)qkv, (const WT*)q_w, (const WT*)k_w, inv_freq, positions, slots, (T*)k_cache, (T*)v_cache, H, KV, page_size, eps)
 #define LAUNCH(T, WT) do { \

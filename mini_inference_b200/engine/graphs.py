@@ -3,7 +3,9 @@
 The reference does the same for its decode steps (engine/core/cuda_graphs.py:8-139): fixed
 device buffers, pinned staging, one graph per bucket, rows beyond the live batch padded with
 harmless work (token 0, position 0, a one-key context on a scratch page).  Differences here:
-all metadata of a step travels in ONE pinned buffer and one copy; sampling is inside the
+all metadata of a step travels in ONE pinned buffer and one copy, laid out and filled by the
+same builder as an eager step's (engine/batch.py: BatchBuilder.static / refill); the block
+tables stay on the device and only their changed entries ride along; sampling is inside the
 graph, so a step returns token ids, not logits; padding rows use the cache's null page 0,
 which no request ever owns.  The number of key splits of the attention kernel is fixed per
 bucket from the longest sequence the cache admits, so the grid depends on the bucket only
@@ -12,51 +14,10 @@ from __future__ import annotations
 
 from typing import List, Optional
 
-import numpy as np
 import torch
 
-from ..parts.base import StepContext
-from .batch import GroupMeta
 
 DEFAULT_BUCKETS = [1, 2, 4, 8, 12, 16, 24, 32, 40, 48, 56, 64, 80, 96, 112, 128, 160, 192, 224, 256]
-
-
-class _StaticBatch:
-    """The StepBatch of a decode-only step of exactly `bucket` rows, as views into one fixed
-    device buffer that a pinned host buffer of the same layout is copied into before a replay."""
-
-    def __init__(self, bucket: int, cache, device, max_kv_len: int, tile: int):
-        B = bucket
-        self.bucket = B
-        self.num_tokens = self.num_segs = self.num_decode = self.num_logit_rows = B
-        self.num_prefill_tiles = 0
-        self.tile = tile
-        self.max_kv_len = max_kv_len                  # fixes the split count for this bucket
-        self.max_q_len = 1
-        P = cache.max_pages_per_seq
-        G = len(cache.kv_groups)
-        fields = [("token_ids", B), ("positions", B), ("seg_pos0", B), ("seg_kv_len", B), ("seg_slot", B),
-                  ("temps", B), ("seeds", B), ("counters", B)]
-        fields += [(f"slots{g}", B) for g in range(G)] + [(f"table{g}", B * P) for g in range(G)]
-        self.offsets, total = {}, 0
-        for name, n in fields:
-            self.offsets[name] = (total, n)
-            total += (n + 3) // 4 * 4
-        self.size = total
-        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
-        ar = torch.arange(B + 1, dtype=torch.int32, device=device)
-        self.token_seg = self.decode_segs = self.logit_rows = ar[:B]
-        self.seg_q_start = ar
-        self.prefill_tiles = torch.zeros((0, 2), dtype=torch.int32, device=device)
-        for name in ("token_ids", "positions", "seg_pos0", "seg_kv_len", "seg_slot", "seeds", "counters"):
-            setattr(self, name, self.view(name))
-        self.temps = self.view("temps").view(torch.float32)
-        self.groups = [GroupMeta(self, cache.page_size, self.view(f"slots{g}"), self.view(f"table{g}").view(B, P), P)
-                       for g in range(G)]
-
-    def view(self, name, buf=None):
-        a, n = self.offsets[name]
-        return (self.dev if buf is None else buf)[a:a + n]
 
 
 class DecodeGraphs:
@@ -64,19 +25,18 @@ class DecodeGraphs:
 
     def __init__(self, runner, max_batch: int, buckets: Optional[List[int]] = None):
         self.runner, self.cache, self.ops = runner, runner.cache, runner.ops
+        self.builder = runner.builder
         self.device = runner.device
         self.buckets = [b for b in (buckets or DEFAULT_BUCKETS) if b < max_batch] + [max_batch]
         self.max_batch = max_batch
         self.batches, self.graphs, self.tokens_out, self.launches = {}, {}, {}, {}
-        self.staging, self.events, self._turn = {}, {}, {}
         self.out_host, self._out_turn = {}, {}
         self.replays = self.eager_steps = 0
         self.capture_s = 0.0
 
     # ---------------------------------------------------------------- capture
     def _forward(self, batch):
-        ctx = StepContext(self.ops, batch, self.runner.dtype, self.device)
-        logits = self.runner.model.forward(ctx, self.cache.layer_caches)
+        logits = self.runner.forward(batch)
         return self.ops.sample(logits, batch.temps, batch.seeds, batch.counters)
 
     def capture(self):
@@ -85,13 +45,9 @@ class DecodeGraphs:
         max_len = self.cache.max_pages_per_seq * self.cache.page_size
         pool = None
         for B in sorted(self.buckets, reverse=True):            # largest first: smaller graphs reuse its pool
-            batch = _StaticBatch(B, self.cache, self.device, max_len, self.ops.prefill_tile)
-            batch.view("seg_kv_len").fill_(1)                    # harmless rows: one key on the null page
-            self.staging[B] = [torch.zeros(batch.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+            batch = self.builder.static(B, max_len)              # harmless rows: one key on the null page
             self.out_host[B] = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
             self._out_turn[B] = 0
-            self.events[B] = [None] * self.RING
-            self._turn[B] = 0
             side = torch.cuda.Stream(self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
@@ -119,49 +75,9 @@ class DecodeGraphs:
     def fill(self, B, seqs, tokens, temps=None, seeds=None, counters=None):
         """Write one decode step's metadata for the live rows (and padding) into the next pinned
         buffer and start its copy.  tokens=None keeps the token ids already on the device (the
-        previous step's samples, see feed_back)."""
-        batch = self.batches[B]
-        turn = self._turn[B]
-        self._turn[B] = (turn + 1) % self.RING
-        if self.events[B][turn] is not None:
-            self.events[B][turn].synchronize()                   # its last copy has left the buffer
-        host = self.staging[B][turn]
-        h = host.numpy()
-        n = len(seqs)
-        pos = np.fromiter((s.num_tokens for s in seqs), dtype=np.int32, count=n)
-
-        def put(name, values, pad):
-            a, m = batch.offsets[name]
-            h[a:a + n] = values
-            h[a + n:a + B] = pad
-        put("positions", pos, 0)
-        put("seg_pos0", pos, 0)
-        put("seg_kv_len", pos + 1, 1)
-        put("seg_slot", [s.slot for s in seqs], 0)
-        a, _ = batch.offsets["temps"]
-        h[a:a + B] = 0
-        if temps is not None:
-            h[a:a + n] = np.asarray(temps, dtype=np.float32).view(np.int32)
-            put("seeds", np.asarray(seeds, dtype=np.uint32).view(np.int32), 0)
-            put("counters", np.asarray(counters, dtype=np.int32), 0)
-        P = self.cache.max_pages_per_seq
-        for g in range(len(self.cache.kv_groups)):
-            put(f"slots{g}", [self.cache.slots_for(g, s, int(p), int(p) + 1)[0] for s, p in zip(seqs, pos)], 0)
-            a, _ = batch.offsets[f"table{g}"]
-            h[a:a + n * P] = self.cache.table_rows(g, seqs, P).reshape(-1)
-            h[a + n * P:a + B * P] = 0
-        a_tok, _ = batch.offsets["token_ids"]
-        end = a_tok + (B + 3) // 4 * 4
-        if tokens is not None:
-            h[a_tok:a_tok + n] = tokens
-            h[a_tok + n:a_tok + B] = 0
-            batch.dev.copy_(host, non_blocking=True)
-        else:                                                    # everything but the token ids
-            batch.dev[end:].copy_(host[end:], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
-        self.events[B][turn] = ev
-        return batch.size * 4 if tokens is not None else (batch.size - end) * 4
+        previous step's samples, see feed_back).  Returns the bytes copied."""
+        sampling = None if temps is None else (temps, seeds, counters)
+        return self.builder.refill(self.batches[B], seqs, tokens, sampling)
 
     def feed_back(self, B):
         """Next step's token ids = this step's samples, without leaving the device."""

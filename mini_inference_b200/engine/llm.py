@@ -7,6 +7,7 @@ add_request() / step() / has_work(), or generate() for a list of prompts.  Token
 native interface (there is no tokenizer in this engine)."""
 from __future__ import annotations
 
+import contextlib
 import time
 from typing import List, Optional, Sequence, Union
 
@@ -17,9 +18,9 @@ from ..config.engine_args import EngineArgs
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
 from .factory import DTYPES, load_model
-from .request import FINISHED, RUNNING, Request, SamplingParams
+from .request import RUNNING, Request, SamplingParams
 from .runner import ModelRunner
-from .scheduler import Scheduler
+from .scheduler import Scheduler, Span
 
 
 class LLM:
@@ -52,7 +53,7 @@ class LLM:
         self.max_model_len = min(self.model.spec.max_position, args.max_model_len)
         needs = self.model.cache_needs()
         probe = CacheManager(needs, args.kv_block_size, 1, 1, args.kv_block_size, dtype=self.dtype, allocate=False)
-        tokens = self._kv_budget_tokens(probe.bytes_per_token())
+        tokens = self._kv_budget_tokens(probe.bytes_per_token(), args.max_num_seqs * probe.state_bytes_per_seq())
         num_pages = max(1, tokens // args.kv_block_size)
         self.cache = CacheManager(needs, args.kv_block_size, num_pages, args.max_num_seqs,
                                   min(self.max_model_len, num_pages * args.kv_block_size),
@@ -87,18 +88,19 @@ class LLM:
         self.graphs.capture()
         self.args.cuda_graphs = True
 
-    def _kv_budget_tokens(self, bytes_per_token: int) -> int:
+    def _kv_budget_tokens(self, bytes_per_token: int, state_bytes: int = 0) -> int:
         """engine/custom_engine.py:105-121: fixed token count, fixed megabytes, or what the GPU
-        has left after the weights and a reserve for activations."""
+        has left after the weights and a reserve for activations.  A memory budget first pays for the
+        fixed-size state of max_num_seqs requests (state_bytes); pages get the rest."""
         a = self.args
         if a.kv_cache_tokens:
             return a.kv_cache_tokens
         if a.kv_cache_mb:
-            return int(a.kv_cache_mb * 1024 ** 2 // max(bytes_per_token, 1))
+            return int(max(a.kv_cache_mb * 1024 ** 2 - state_bytes, 0) // max(bytes_per_token, 1))
         if self.device.type != "cuda":
             return 32768
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = total * a.gpu_memory_utilization - (total - free) - a.activation_reserve_gb * 1024 ** 3
+        budget = total * a.gpu_memory_utilization - (total - free) - a.activation_reserve_gb * 1024 ** 3 - state_bytes
         return max(int(max(budget, 0) // max(bytes_per_token, 1)), 1024)
 
     # ---------------------------------------------------------------- requests
@@ -140,10 +142,11 @@ class LLM:
                 return self._fail_unschedulable()
             handle = None
             try:
-                if self.graphs is not None and self.graphs.can_run(chunks):
-                    handle = self.graphs.launch(chunks, self.sampler)
-                else:
-                    tokens = self._run(chunks)
+                with self._label(chunks):
+                    if self.graphs is not None and self.graphs.can_run(chunks):
+                        handle = self.graphs.launch(chunks, self.sampler)
+                    else:
+                        tokens = self._run(chunks)
             except Exception as e:
                 return self._abort(e)
             if handle is None:
@@ -176,7 +179,7 @@ class LLM:
         for req, _, end in chunks:
             if not self.cache.ensure(req.seq, end + 1):
                 return None                                              # out of pages: the scheduler decides who yields
-        ahead = [(req, end, end + 1) for req, _, end in chunks]
+        ahead = [Span(req, end, end + 1) for req, _, end in chunks]
         self.scheduler.count_decode_step(len(ahead))
         return ahead, self.graphs.launch(ahead, self.sampler, on_device_tokens=True)
 
@@ -191,7 +194,7 @@ class LLM:
         self._ahead = None
         done = self.scheduler.abort_all()
         for r in done:
-            self._finish(r, "error", error=self.last_error)
+            r.close("error", error=self.last_error)
         return done
 
     def _deliver(self, chunks, tokens) -> List[Request]:
@@ -206,14 +209,11 @@ class LLM:
                 continue
             tok = tokens[row]
             row += 1
-            req.output_ids.append(tok)
-            if req.first_token_at is None:
-                req.first_token_at = now
-            req.token_times.append(now)
+            req.deliver(tok, now)
             eos = tok in self.eos_ids and not req.params.ignore_eos
             if eos or len(req.output_ids) >= req.params.max_new_tokens or req.total_len >= self.max_model_len:
                 self.scheduler.finish(req)
-                self._finish(req, "stop" if eos else "length")
+                req.close("stop" if eos else "length")
                 done.append(req)
         return done
 
@@ -225,7 +225,7 @@ class LLM:
         entries, sampled = [], []
         for req, s, e in chunks:
             last = e == req.total_len
-            entries.append(StepEntry(req.seq, req.all_ids[s:e], [e - s - 1] if last else []))
+            entries.append(StepEntry(req.seq, req.span(s, e), [e - s - 1] if last else []))
             if last:
                 sampled.append(req)
         logits = self.runner.step(entries, ensure=False)
@@ -233,9 +233,14 @@ class LLM:
             return []
         return self.sampler.sample(logits, sampled).tolist()             # the step's one device->host sync
 
-    def _finish(self, req, reason, error=None):
-        req.state, req.finish_reason, req.error = FINISHED, reason, error
-        req.finished_at = time.perf_counter()
+    def _label(self, plan):
+        """A profiler range per step, in the reference's wording (engine/core/model_runner.py:98-102):
+        forward(T=tokens, decode=rows, prefill=rows, ctx=keys).  Only with NVTX=1 (the reference's switch)."""
+        if not self.args.nvtx or self.device.type != "cuda":
+            return contextlib.nullcontext()
+        dec = sum(1 for s in plan if s.is_decode)
+        return torch.cuda.nvtx.range(f"forward(T={plan.num_tokens}, decode={dec}, prefill={len(plan) - dec}, "
+                                     f"ctx={sum(s.end for s in plan)})")
 
     def _fail_unschedulable(self):
         """Nothing could be scheduled.  If nothing runs either, the request at the head of the
@@ -244,8 +249,8 @@ class LLM:
         if self.scheduler.running or not self.scheduler.waiting:
             return []
         req = self.scheduler.waiting.popleft()
-        self._finish(req, "error", error=f"request of {req.total_len} tokens does not fit in the cache "
-                                         f"({self.cache.capacity_tokens} tokens)")
+        req.close("error", error=f"request of {req.total_len} tokens does not fit in the cache "
+                                 f"({self.cache.capacity_tokens} tokens)")
         return [req]
 
     # ---------------------------------------------------------------- public API

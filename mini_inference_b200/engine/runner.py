@@ -10,7 +10,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..parts.base import StepContext
 from ..parts.model import DecoderModel
-from .batch import StepBatch, StepEntry
+from .batch import BatchBuilder, StepBatch, StepEntry
 
 
 class CacheFull(RuntimeError):
@@ -27,6 +27,9 @@ class ModelRunner:
         self.model, self.cache, self.ops = model, cache, ops
         self.device, self.dtype = model.device, model.dtype
         self.vocab_size = model.spec.vocab_size
+        self.builder = BatchBuilder(cache, self.device, model.step_array_hooks(), tile=getattr(ops, "prefill_tile", 64),
+                                    vocab_size=self.vocab_size)
+        self.builder.ops = ops
         self.last_batch: Optional[StepBatch] = None
 
     @torch.inference_mode()
@@ -46,11 +49,15 @@ class ModelRunner:
                 end = e.seq.num_tokens + len(e.tokens)
                 if not self.cache.ensure(e.seq, end):
                     raise CacheFull(f"no pages left for request {e.seq.seq_id!r} to reach {end} tokens")
-        batch = StepBatch(entries, self.cache, self.device, tile=getattr(self.ops, "prefill_tile", 64),
-                          vocab_size=self.vocab_size)
+        batch = self.builder.build(entries)
         self.last_batch = batch
-        ctx = StepContext(self.ops, batch, self.dtype, self.device)
-        logits = self.model.forward(ctx, self.cache.layer_caches)
+        logits = self.forward(batch)
         for e in entries:
             self.cache.commit(e.seq, e.seq.num_tokens + len(e.tokens))
         return logits
+
+    def forward(self, batch: StepBatch):
+        """The device work of a step whose batch is built: block-table changes first, then the model."""
+        batch.apply_table_updates(self.ops)
+        ctx = StepContext(self.ops, batch, self.dtype, self.device)
+        return self.model.forward(ctx, self.cache.layer_caches)

@@ -35,8 +35,8 @@ def build_spec(cfg: Qwen3Config) -> ModelSpec:
             "feed_forward.up_proj": p + "mlp.up_proj.weight",
             "feed_forward.down_proj": p + "mlp.down_proj.weight",
         }
-        layers.append(LayerSpec(block="prenorm", mixer=mixer, feed_forward=feed_forward, norm=norm,
-                                position=position, weight_names=tuple(sorted(names.items()))))
+        layers.append(LayerSpec.of("prenorm", names, mixer=mixer, feed_forward=feed_forward, norm1=norm, norm2=norm,
+                                   position=position))
     return ModelSpec(
         hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=tuple(layers),
         order=tuple(ExecStep(i) for i in range(cfg.num_hidden_layers)),

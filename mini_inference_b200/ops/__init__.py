@@ -75,7 +75,7 @@ class CudaOps:
     prefill_tile = 64
     deferred = True                          # linear(..., defer=True) may answer with a DeferredSum
     takes_hints = True                       # add_rmsnorm(..., next_weight=) is understood
-    NUM_SMS = 148
+    MAX_ROWS = 4096                          # decode rows x kv heads that the attention merge counters cover
 
     def __init__(self, device):
         self.device = torch.device(device)
@@ -84,13 +84,15 @@ class CudaOps:
                                f"device '{device}' is not one")
         self.lib = load_library()
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.NUM_SMS = torch.cuda.get_device_properties(self._device_index).multi_processor_count
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
         self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"      # many-row products on the tcgen05 kernel
         self.tc_min_rows = 128
         self.tc_attention = os.environ.get("MI_TC_ATTENTION", "1") == "1"    # prompt attention on the tcgen05 kernel
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
-        self._sample_slots = self._sample_arrivals = None
+        self._sample_slots = torch.zeros(4096, dtype=torch.int64, device=self.device)
+        self._sample_arrivals = torch.zeros(4096, dtype=torch.int32, device=self.device)
         # decode attention stages K/V through shared memory with swizzled TMA tiles and per-warp mbarrier rings (31 vs
         # 33 us at batch 8, 168 vs 202 us at batch 64, context 4096, against streaming them into registers);
         # MI_BULK_DECODE=0 selects the register-streaming variant
@@ -98,14 +100,14 @@ class CudaOps:
         self.fused_merge = True              # the last split block to finish merges the splits (no merge launch)
         # 2..8 splits of a (request, kv head): one thread-block cluster, merged through distributed shared memory
         self.cluster_merge = os.environ.get("MI_CLUSTER_MERGE", "1") == "1"
-        # q/k norm + rotation + cache write inside the decode attention kernel's preamble (one launch less per layer).
-        # Measured no faster (3.30 vs 3.30 ms at batch 8, 2.78 vs 2.73 ms at batch 1): the separate kernel's time is
-        # hidden by programmatic launch (attention requests its first K/V tiles while it runs), the preamble's is not.
-        self.fuse_qk = os.environ.get("MI_FUSE_QK", "0") == "1"
-        self._merge_counters = None
         self._cluster_fit = {}
         self._linear_choice = None           # {(row bucket, N, K): "library" | "stream" | "skinny"} from tune_linear
-        self._stream_plans, self._stream_counters, self._stream_error = {}, None, None
+        self._stream_plans = {}
+        # Scratch that kernels address directly and that captured graphs keep the address of: allocated here, once, at
+        # fixed sizes; a call that needs more raises instead of moving them.
+        self._merge_counters = torch.zeros(self.MAX_ROWS * 8, dtype=torch.int32, device=self.device)
+        self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self._stream_error = torch.zeros(1, dtype=torch.int32, device=self.device)
         # a few-row product whose only reader is the next residual-add + norm is left as partial sums for that kernel
         # to add up (no fix-up tail in the GEMM); MI_DEFER_SUMS=0 turns it off
         self.defer_sums = os.environ.get("MI_DEFER_SUMS", "1") == "1"
@@ -116,11 +118,6 @@ class CudaOps:
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
-        # few rows: out-projection, norm and feed-forward of a block as one persistent kernel (csrc/decode_chain.cu).
-        # Measured at Qwen3-4B sizes, 8 rows: 52 us against ~50 us for the separate kernels (its three products run
-        # at 5.9 TB/s, but five grid-wide barriers and the passes between them cost ~20 us), so it is off unless asked for.
-        self.decode_chain_on = os.environ.get("MI_DECODE_CHAIN", "0") == "1"
-        self._chain_plans, self._chain_state = {}, None
         self.launches = 0                    # kernels of this package launched so far
 
     def _stream(self):
@@ -129,6 +126,14 @@ class CudaOps:
         return _c.c_void_p(_raw_stream(self._device_index))
 
     # ---------------------------------------------------------------- elementwise / norms
+    def scatter_i32(self, table, idx, val):
+        """table[idx[i]] = val[i]: the block-table entries that changed since the last step (cache/manager.py)."""
+        n = idx.shape[0]
+        if n:
+            _check(self.lib.mi_scatter_i32(_p(table), _p(idx), _p(val), n, _c.c_longlong(table.numel()), self._stream()),
+                   "scatter_i32")
+            self.launches += 1
+
     def embedding(self, ids, table):
         T, hidden = ids.shape[0], table.shape[1]
         out = torch.empty((T, hidden), dtype=table.dtype, device=table.device)
@@ -172,9 +177,6 @@ class CudaOps:
         inter = w.shape[0] // 2
         if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
-            if self._stream_error is None:
-                self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
-                self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
             act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
             rc = self.lib.mi_gemm_tc_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
             if rc == 0:
@@ -338,9 +340,8 @@ class CudaOps:
         if not plan:
             return None
         grid, row_tiles, max_contrib = plan
-        if self._stream_counters is None or self._stream_counters.numel() < row_tiles:
-            self._stream_counters = torch.zeros(max(row_tiles, 4096), dtype=torch.int32, device=x.device)
-            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
+        if row_tiles > self._stream_counters.numel():
+            return None                      # more row tiles than the fixed counters cover: another kernel takes it
         tok = 8 if M <= 8 else 16 if M <= 16 else 32
         workspace = torch.empty(row_tiles * max_contrib * 128 * tok, dtype=torch.float32, device=x.device)
         if defer:
@@ -364,9 +365,6 @@ class CudaOps:
         """tcgen05 + TMA product for many rows (csrc/gemm_tc.cu); None if the shape is not taken."""
         M, K = x.shape
         N = w.shape[0]
-        if self._stream_error is None:
-            self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
-            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
         out = torch.empty((M, N), dtype=od, device=x.device)
         rc = self.lib.mi_gemm_tc(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), _p(self._stream_error),
                                  self._stream())
@@ -376,49 +374,12 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def decode_chain(self, attn, w_out, x, norm_w, eps, w_gate_up, w_down):
-        """x += attn @ w_out.T; returns (silu(g) * u) @ w_down.T with [g | u] = rmsnorm(x) @ w_gate_up.T, all in
-        one launch, or None when these sizes or dtypes are not taken (the caller then runs the separate kernels)."""
-        M, q_dim = attn.shape
-        hidden, inter = x.shape[1], w_down.shape[1]
-        tensors = (attn, w_out, x, norm_w, w_gate_up, w_down)
-        if (not self.decode_chain_on or M > 16 or any(t.dtype != torch.bfloat16 for t in tensors)
-                or not (x.is_contiguous() and w_out.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous())
-                or attn.stride(1) != 1 or attn.stride(0) % 8):
-            return None
-        key = (8 if M <= 8 else 16, hidden, q_dim, inter)
-        plan = self._chain_plans.get(key)
-        if plan is None:
-            ws = _c.c_longlong()
-            rc = self.lib.mi_decode_chain_plan(key[0], hidden, q_dim, inter, _c.byref(ws))
-            plan = self._chain_plans[key] = False if rc else ws.value
-        if not plan:
-            return None
-        ws_floats = plan
-        if self._chain_state is None:        # allocated once: captured graphs keep this address
-            self._chain_state = torch.zeros(1, dtype=torch.int64, device=x.device)
-        if self._stream_error is None:
-            self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=x.device)
-            self._stream_error = torch.zeros(1, dtype=torch.int32, device=x.device)
-        workspace = torch.empty(ws_floats, dtype=torch.float32, device=x.device)
-        gate_up = torch.empty((M, 2 * inter), dtype=torch.bfloat16, device=x.device)
-        act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
-        out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
-        rc = self.lib.mi_decode_chain(_p(attn), attn.stride(0), _p(w_out), _p(x), x.stride(0), _p(norm_w), _c.c_float(eps),
-                                      _p(w_gate_up), _p(gate_up), _p(w_down), _p(act), _p(out), M, hidden, q_dim, inter,
-                                      _p(workspace), _p(self._chain_state), _p(self._stream_error), self._stream())
-        if rc == -2:
-            return None
-        _check(rc, "decode_chain")
-        self.launches += 1
-        return out
-
     def check_errors(self):
         """Raises if a bounded wait inside a kernel ran out (synchronises the device)."""
-        if self._stream_error is not None and int(self._stream_error.item()) != 0:
-            code = int(self._stream_error.item())
+        code = int(self._stream_error.item())
+        if code != 0:
             self._stream_error.zero_()
-            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention, 41-45 decode_chain)")
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):
@@ -467,91 +428,81 @@ class CudaOps:
         return best
 
     def qk_attention(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache, owns_cache, scale, window):
-        """Per-head q/k norm, rotation, cache write, then attention over the pages.  When every row of the step is a
-        decoded token the first three happen in the attention kernel's preamble (one launch less per layer)."""
-        T = qkv.shape[0]
-        if (self.fuse_qk and self.bulk_decode and self.fast_attention and meta.num_decode == T and not meta.num_prefill_tiles
-                and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and D in (64, 128) and H // KV <= 16
-                and meta.page_size % 16 == 0 and all(w is None or w.dtype == torch.bfloat16 for w in (q_weight, k_weight))):
-            return self.paged_attention(None, k_cache, v_cache, meta, H, KV, D, scale, window,
-                                        fused=(qkv, q_weight, k_weight, eps, inv_freq, owns_cache))
+        """Per-head q/k norm, rotation, cache write, then attention over the pages."""
         q = self.qk_norm_rope_cache(qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta,
                                     k_cache if owns_cache else None, v_cache if owns_cache else None)
         return self.paged_attention(q, k_cache, v_cache, meta, H, KV, D, scale, window)
 
-    def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window, fused=None):
-        if fused is not None:                # q is still inside qkv (see qk_attention): only decoded tokens, fast kernel
-            q = fused[0][:, :H * D]
+    def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
+        """meta: the step's arrays for this cache group.  seg_q_start, seg_pos0, seg_kv_len per entry; decode_segs (entries
+        that feed one token), prefill_tiles / prefill_tiles2 ((entry, first row) per tile of meta.tile / 2 * meta.tile query
+        rows); block_table [rows, max_pages] with entry i reading row table_rows[i] (row i when table_rows is None)."""
         T = q.shape[0]
         assert q.stride(1) == 1
         out = torch.empty((T, H * D), dtype=q.dtype, device=q.device)
         code, win = _code(q.dtype), int(window or 0)
+        rows = getattr(meta, "table_rows", None)
+        num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
+        tiles2 = getattr(meta, "prefill_tiles2", None)
+        num_tiles2 = 0 if tiles2 is None else tiles2.shape[0]
         fast = (self.fast_attention and q.dtype == torch.bfloat16 and D in (64, 128) and q.stride(0) % 8 == 0
                 and q.data_ptr() % 16 == 0)
-        tc = (fast and self.tc_attention and meta.num_prefill_tiles and meta.tile == 64 and meta.page_size % 8 == 0
-              and 64 % meta.page_size == 0 and getattr(meta, "num_prefill_tiles2", 0))
+        tc = (fast and self.tc_attention and num_tiles and meta.tile == 64 and meta.page_size % 8 == 0
+              and 64 % meta.page_size == 0 and num_tiles2)
         if tc:
-            if self._stream_error is None:
-                self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
-                self._stream_error = torch.zeros(1, dtype=torch.int32, device=q.device)
             rc = self.lib.mi_attn_prefill_tc(
                 _p(q), q.stride(0), T, _p(k_cache), _p(v_cache), _c.c_longlong(k_cache.shape[0] * KV * meta.page_size),
-                _p(out), _p(meta.prefill_tiles2), meta.num_prefill_tiles2, _p(meta.seg_q_start), _p(meta.seg_pos0),
-                _p(meta.block_table), meta.max_pages, H, KV, D, meta.page_size, 128, _c.c_float(scale), win,
+                _p(out), _p(tiles2), num_tiles2, _p(meta.seg_q_start), _p(meta.seg_pos0),
+                _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, 128, _c.c_float(scale), win,
                 _p(self._stream_error), self._stream())
             _check(rc, "attn_prefill_tc")
             self.launches += 1
-        elif meta.num_prefill_tiles and fast and meta.tile == 64:
+        elif num_tiles and fast and meta.tile == 64:
             _check(self.lib.mi_attn_prefill_mma(
-                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
-                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles,
+                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D,
                 meta.page_size, meta.tile, _c.c_float(scale), win, self._stream()), "attn_prefill_mma")
             self.launches += 1
-        elif meta.num_prefill_tiles:
+        elif num_tiles:
             _check(self.lib.mi_attn_prefill_generic(
-                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), meta.num_prefill_tiles,
-                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), meta.max_pages, H, KV, D,
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles,
+                _p(meta.seg_q_start), _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D,
                 meta.page_size, meta.tile, _c.c_float(scale), win, code, self._stream()), "attn_prefill")
             self.launches += 1
+        if not num_decode:
+            return out
         fast_decode = fast and H // KV <= 16 and meta.page_size % 16 == 0
-        if meta.num_decode:
-            S = self.choose_splits(meta.num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len,
-                                   (2 if self.bulk_decode else 3) if fast_decode else 2,
-                                   cluster=fast_decode and self.bulk_decode and self.cluster_merge, head_dim=D)
-            o_part = lse = None
-            if S > 1:
-                o_part = torch.empty((meta.num_decode, H, S, D), dtype=torch.float32, device=q.device)
-                lse = torch.empty((meta.num_decode, H, S), dtype=torch.float32, device=q.device)
-        if meta.num_decode and fast_decode:
+        S = self.choose_splits(num_decode * (KV if fast_decode else math.ceil(H / 4)), meta.max_kv_len,
+                               (2 if self.bulk_decode else 3) if fast_decode else 2,
+                               cluster=fast_decode and self.bulk_decode and self.cluster_merge, head_dim=D)
+        o_part = lse = None
+        if S > 1:
+            o_part = torch.empty((num_decode, H, S, D), dtype=torch.float32, device=q.device)
+            lse = torch.empty((num_decode, H, S), dtype=torch.float32, device=q.device)
+        if fast_decode:
             counters = None
             if S > 1 and self.fused_merge:
-                need = meta.num_decode * KV
-                if self._merge_counters is None or self._merge_counters.numel() < need:
-                    self._merge_counters = torch.zeros(max(need, 8192), dtype=torch.int32, device=q.device)
+                if num_decode * KV > self._merge_counters.numel():
+                    raise ValueError(f"attn_decode: {num_decode} rows x {KV} kv heads exceed the {self._merge_counters.numel()} "
+                                     "merge counters allocated at start-up")
                 counters = self._merge_counters
-            err_word = None
-            if self.bulk_decode:
-                if self._stream_error is None:
-                    self._stream_counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
-                    self._stream_error = torch.zeros(1, dtype=torch.int32, device=q.device)
-                err_word = self._stream_error
-            qkv, q_w, k_w, eps, inv_freq, owns = fused if fused is not None else (None, None, None, 0.0, None, False)
-            _check(self.lib.mi_attn_decode_mma_qk(
+            # without counters the splits stay in o_part / lse for the merge launch below: the cluster merge must be off too
+            cluster = int(self.cluster_merge and counters is not None)
+            _check(self.lib.mi_attn_decode_mma_rows(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
-                meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
-                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters), _p(err_word), k_cache.shape[0],
-                _p(qkv), _p(q_w), _p(k_w), _p(inv_freq), _p(meta.positions if fused is not None else None),
-                _p(meta.slots if fused is not None else None), int(bool(owns)),
-                _c.c_float(eps), int(self.cluster_merge), self._stream()), "attn_decode_mma")
+                num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages,
+                H, KV, D, meta.page_size, S, _c.c_float(scale), win, _p(counters),
+                _p(self._stream_error if self.bulk_decode else None), k_cache.shape[0], cluster, self._stream()),
+                "attn_decode_mma")
             self.launches += 1
             if S > 1 and counters is None:
-                _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), meta.num_decode,
+                _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), num_decode,
                                                      _p(meta.seg_q_start), H, D, S, code, self._stream()), "attn_merge")
                 self.launches += 1
-        elif meta.num_decode:
+        else:
             _check(self.lib.mi_attn_decode_generic(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs),
-                meta.num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), meta.max_pages,
+                num_decode, _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages,
                 H, KV, D, meta.page_size, S, _c.c_float(scale), win, code, self._stream()), "attn_decode")
             self.launches += 2 if S > 1 else 1
         return out
@@ -567,9 +518,6 @@ class CudaOps:
         R, V = logits.shape
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
         if V >= 16384 and R <= 4096:                     # several blocks per row
-            if self._sample_slots is None:
-                self._sample_slots = torch.zeros(4096, dtype=torch.int64, device=logits.device)
-                self._sample_arrivals = torch.zeros(4096, dtype=torch.int32, device=logits.device)
             _check(self.lib.mi_sample_split(_p(logits), logits.stride(0), R, V, _p(temperatures), _p(seeds), _p(counters),
                                             _p(out), _p(self._sample_slots), _p(self._sample_arrivals), self._stream()),
                    "sample")

@@ -7,6 +7,7 @@ the step's pages BEFORE attention runs, so a portion attends to itself through t
 (:156).  Attention reads the pages in place for prompt portions and decoded tokens alike."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from .base import KVCacheNeed, Part, WeightSpec, register_mixer
@@ -14,6 +15,9 @@ from .base import KVCacheNeed, Part, WeightSpec, register_mixer
 
 @register_mixer("gqa_attention")
 class GQAAttention(Part):
+    offers_open = True
+    step_arrays_key = "paged_attention"
+
     def __init__(self, spec):
         super().__init__(spec)
         g = spec.get
@@ -47,6 +51,22 @@ class GQAAttention(Part):
     def open_weight(self):
         return self.o
 
+    @property
+    def first_weight(self):
+        return self.qkv
+
+    def step_arrays(self, facts):
+        """The attention kernels' work lists: the entries that feed one token (decode kernel), and for the longer
+        entries one (entry, first row) pair per tile of query rows (prompt kernels; the tensor-core kernel takes
+        tiles twice as tall)."""
+        lens, tile = facts.lens, facts.tile
+        decode = [i for i, n in enumerate(lens) if n == 1]
+        tiles = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, tile)]
+        tiles2 = [(i, r) for i, n in enumerate(lens) if n > 1 for r in range(0, n, 2 * tile)]
+        as_i32 = lambda v, shape: np.asarray(v, dtype=np.int32).reshape(shape)      # noqa: E731
+        return {"decode_segs": as_i32(decode, (-1,)), "prefill_tiles": as_i32(tiles, (-1, 2)),
+                "prefill_tiles2": as_i32(tiles2, (-1, 2))}
+
     def forward(self, h, ctx, cache, position, owns_cache=True):
         o, w = self.forward_open(h, ctx, cache, position, owns_cache)
         return ctx.ops.linear(o, w)
@@ -54,7 +74,7 @@ class GQAAttention(Part):
     def forward_open(self, h, ctx, cache, position, owns_cache=True):
         """Everything but the output projection: (attention rows [T, H*D], o_proj weight)."""
         ops = ctx.ops
-        meta = ctx.batch.groups[cache.group]
+        meta = ctx.batch.group_view(cache.group, self.step_arrays_key)
         qkv = ops.linear(h, self.qkv)
         o = ops.qk_attention(qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
                              position.rotary_inv_freq(), meta, cache.k, cache.v, owns_cache, self.scale, self.window)

@@ -1,9 +1,10 @@
 """Interfaces and registries of the parts a decoder layer is assembled from.
 
 A part (mixer, feed-forward, norm, position encoding, block arrangement) is a class
-registered under a name.  It is built from its own PartSpec (sizes and constants), names
-the tensors it needs in its own terms, and computes through the kernel namespace handed to
-it in the StepContext.  It never sees the model's configuration or its neighbours' specs.
+registered under a name in the registry of its family.  It is built from its own PartSpec
+(sizes and constants), names the tensors it needs in its own terms, and computes through the
+kernel namespace handed to it in the StepContext.  It never sees the model's configuration
+or its neighbours' specs.
 
 Interfaces
   every part   __init__(spec)            sizes/constants from spec only
@@ -19,22 +20,33 @@ Interfaces
   Mixer        cache_need() -> KVCacheNeed | StateNeed | None
                forward(h, ctx, cache, position, owns_cache) -> [T, hidden]
                    cache is the LayerCache of the execution step (or of the step it reads)
-  Block        __init__(spec, mixer, feed_forward, norm1, norm2, position)
+  Block        roles = {role: family}    the parts it arranges; the model builds one part per role from
+                                         LayerSpec.parts and hands them over as a dict
+               __init__(spec, parts)
+               mixer                     the part whose cache_need() the cache manager serves
                forward(x, delta, ctx, cache, owns_cache) -> (x, delta)
                    x is the residual stream, delta an addition not yet applied to it
 
-Optional fast-path protocol (a block may use what its parts offer; none has to):
-  Mixer        forward_open(h, ctx, cache, position, owns_cache) -> (rows, out_weight)
-                   forward() without its last product: forward == linear(rows, out_weight); open_weight names that tensor
-  FeedForward  forward_open(h, ctx) -> (rows, out_weight)      the same
-  Norm         accepts_deferred = True   when forward hands `delta` to ctx.ops.add_rmsnorm untouched: the block may then
-                   give it the result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
-               rms_params() -> (weight, eps)   when forward is the plain RMS norm
-  FeedForward  gated_weights() -> (gate_up [2I, hidden], down [hidden, I])
-                   when forward == linear(silu(g) * u, down) with [g | u] = linear(h, gate_up)
-  Mixer, FeedForward   first_weight -> the tensor that forward() reads first
-  Norm         takes_next_weight = True   when forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the
-                   block names the first weight of the part that follows the norm, and the kernel may request it into L2
+Per-step arrays of a part's own (any part may offer this; the step builder calls it once per step and key):
+  step_arrays_key = "name"               parts that share a key share the arrays (all attention layers: one work list)
+  step_arrays(facts) -> {name: int32 numpy array}
+                   facts: StepFacts (lens, pos0, kv_len, q_start, slots of the entries; tile size of the kernels).
+                   The arrays travel to the device in the step's one metadata buffer; the part finds them as
+                   ctx.batch.extras[key][name] (device) and ctx.batch.extras_host[key][name] (numpy).  For a given
+                   list of entry lengths the arrays must always have the same sizes (decode steps are replayed
+                   as graphs over fixed buffers).
+
+Optional fast-path protocol.  Every name below is declared on Part with a default that means "not offered";
+a block reads the attributes, it never probes with hasattr:
+  offers_open = True       Mixer: forward_open(h, ctx, cache, position, owns_cache) -> (rows, out_weight)
+                           FeedForward: forward_open(h, ctx) -> (rows, out_weight)
+                               forward() without its last product: forward == linear(rows, out_weight)
+  open_weight              the tensor forward_open returns as out_weight (after load)
+  first_weight             the tensor that forward() streams first (after load)
+  accepts_deferred = True  Norm: forward hands `delta` to ctx.ops.add_rmsnorm untouched, so the block may give it the
+                               result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
+  takes_next_weight = True Norm: forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the block
+                               names the first weight of the part that follows, and the kernel may request it into L2
 """
 from __future__ import annotations
 
@@ -71,7 +83,7 @@ class StateNeed:
 class LayerCache:
     """What one execution step's mixer gets from the cache manager: for pages, the step's key
     and value pools [pages, kv_heads, page_size, head_dim] and the index of the cache group
-    whose block tables (ctx.batch.groups[group]) address them; for state, the slot tensor."""
+    whose block tables (ctx.batch.group_view(group, ...)) address them; for state, the slot tensor."""
     def __init__(self, group: int, k=None, v=None, state=None):
         self.group, self.k, self.v, self.state = group, k, v, state
 
@@ -85,6 +97,14 @@ class StepContext:
 
 
 class Part:
+    # the optional protocol, declared (see the module text); a subclass overrides what it offers
+    offers_open = False
+    open_weight = None
+    first_weight = None
+    accepts_deferred = False
+    takes_next_weight = False
+    step_arrays_key: Optional[str] = None
+
     def __init__(self, spec: PartSpec):
         self.spec = spec
 
@@ -93,6 +113,9 @@ class Part:
 
     def load(self, tensors, dtype, device):
         pass
+
+    def step_arrays(self, facts):
+        return {}
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
@@ -114,6 +137,8 @@ def register_block(name): return _register("block", name)
 
 
 def lookup(family: str, name: str):
+    if family not in _REGISTRIES:
+        raise KeyError(f"no family of parts named '{family}' (known: {', '.join(sorted(_REGISTRIES))})")
     table = _REGISTRIES[family]
     if name not in table:
         raise KeyError(f"no {family} part named '{name}' is registered (known: {', '.join(sorted(table)) or 'none'})")

@@ -10,6 +10,8 @@ from .base import Part, WeightSpec, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(Part):
+    offers_open = True
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(spec.get("hidden_size"))
@@ -40,6 +42,3 @@ class SwiGLU(Part):
     def forward_open(self, h, ctx):
         """Everything but the last product: (silu(gate) * up, down weight)."""
         return ctx.ops.gated_linear(h, self.gate_up), self.down
-
-    def gated_weights(self):
-        return self.gate_up, self.down

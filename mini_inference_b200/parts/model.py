@@ -8,7 +8,7 @@ from typing import Dict, List, Tuple
 import torch
 
 from ..config.spec import ModelSpec, PartSpec
-from .base import Part, WeightSpec, build_part
+from .base import Part, WeightSpec, build_part, lookup
 
 
 class DecoderModel:
@@ -17,29 +17,34 @@ class DecoderModel:
         self._positions: Dict = {}
         self.blocks = []
         self._owned: List[Tuple[str, WeightSpec, Part]] = []      # (checkpoint name, spec, owner)
-        for layer in spec.layers:
+        for li, layer in enumerate(spec.layers):
             names = dict(layer.weight_names)
-            position = self._positions.get(layer.position)
-            if position is None:                       # one position part per distinct spec, shared by its layers;
-                position = self._positions[layer.position] = build_part("position", layer.position)
-                for ws in position.weight_specs():     # its tensors (if any) are named by the first layer that uses it
-                    key = f"position.{ws.name}"
-                    if key not in names:
-                        raise KeyError(f"the layer's weight_names has no entry for '{key}'")
-                    self._owned.append((names[key], ws, position))
-            mixer = build_part("mixer", layer.mixer)
-            ffn = build_part("feed_forward", layer.feed_forward)
-            norm1, norm2 = build_part("norm", layer.norm), build_part("norm", layer.norm)
-            self.blocks.append(build_part("block", PartSpec.of(layer.block), mixer, ffn, norm1, norm2, position))
-            for role, part in (("mixer", mixer), ("feed_forward", ffn), ("norm1", norm1), ("norm2", norm2)):
+            block_cls = lookup("block", layer.block)
+            given = dict(layer.parts)
+            if set(given) != set(block_cls.roles):
+                raise KeyError(f"layer {li}: block '{layer.block}' arranges the roles {sorted(block_cls.roles)}, "
+                               f"the layer gives {sorted(given)}")
+            parts = {}
+            for role, family in block_cls.roles.items():
+                pspec = given[role]
+                if family == "position":               # one position part per distinct spec, shared by its layers;
+                    part = self._positions.get(pspec)  # its tensors (if any) are named by the first layer that uses it
+                    if part is not None:
+                        parts[role] = part
+                        continue
+                    part = self._positions[pspec] = build_part(family, pspec)
+                else:
+                    part = build_part(family, pspec)
+                parts[role] = part
                 for ws in part.weight_specs():
                     key = f"{role}.{ws.name}"
                     if key not in names:
-                        raise KeyError(f"the layer's weight_names has no entry for '{key}'")
+                        raise KeyError(f"layer {li}: weight_names has no entry for '{key}'")
                     self._owned.append((names[key], ws, part))
+            self.blocks.append(block_cls(PartSpec.of(layer.block), parts))
         self.final_norm = build_part("norm", spec.final_norm)
-        norms = [n for b in self.blocks for n in (b.norm1, b.norm2)] + [self.final_norm]
-        self._norms_accept_deferred = all(getattr(n, "accepts_deferred", False) for n in norms)
+        norms = [p for b in self.blocks for role, p in b.parts.items() if b.roles[role] == "norm"] + [self.final_norm]
+        self._norms_accept_deferred = all(n.accepts_deferred for n in norms)
         for ws in self.final_norm.weight_specs():
             self._owned.append((spec.final_norm_name, ws, self.final_norm))
         self.embedding = None
@@ -81,8 +86,8 @@ class DecoderModel:
         """The matrices the model multiplies by (after the parts fused what they fuse)."""
         out = []
         for block in self.blocks:
-            for part in (block.mixer, block.feed_forward):
-                out += [v for v in vars(part).values() if isinstance(v, torch.Tensor) and v.dim() == 2]
+            for part in block.parts.values():
+                out += [v for v in vars(part).values() if isinstance(v, torch.Tensor) and v.dim() == 2 and v.is_floating_point()]
         out.append(self.lm_head)
         return out
 
@@ -93,11 +98,20 @@ class DecoderModel:
             return frozenset()
         shapes = set()
         for block in self.blocks:
-            for part in (block.mixer, block.feed_forward):
-                w = getattr(part, "open_weight", None)
-                if hasattr(part, "forward_open") and isinstance(w, torch.Tensor) and w.dim() == 2:
+            for part in block.parts.values():
+                w = part.open_weight
+                if part.offers_open and isinstance(w, torch.Tensor) and w.dim() == 2:
                     shapes.add((w.shape[0], w.shape[1]))
         return frozenset(shapes)
+
+    def step_array_hooks(self):
+        """{key: part.step_arrays} of the parts that ask for per-step arrays of their own, one per key."""
+        hooks = {}
+        for block in self.blocks:
+            for part in block.parts.values():
+                if part.step_arrays_key is not None:
+                    hooks.setdefault(part.step_arrays_key, part.step_arrays)
+        return hooks
 
     # ---------------------------------------------------------------- cache needs
     def cache_needs(self):

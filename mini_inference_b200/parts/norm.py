@@ -27,6 +27,3 @@ class RMSNorm(Part):
         if next_weight is not None and ctx.hints_ok:
             return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows, next_weight=next_weight)
         return ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, rows)
-
-    def rms_params(self):
-        return self.weight, self.eps

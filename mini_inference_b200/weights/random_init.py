@@ -19,22 +19,24 @@ from .safetensors_io import write_safetensors
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 
 
-def _draw(ws, seed: int, index: int, std: float, norm_init: str) -> torch.Tensor:
-    g = torch.Generator().manual_seed(seed * 1_000_003 + index)
+def _draw(ws, seed: int, index: int, std: float, norm_init: str, device="cpu") -> torch.Tensor:
+    g = torch.Generator(device=device).manual_seed(seed * 1_000_003 + index)
     if ws.kind == "table":
         return torch.zeros(ws.shape, dtype=torch.int32)
     if ws.init == "norm":
         if norm_init == "ones":
             return torch.ones(ws.shape)
-        return torch.rand(ws.shape, generator=g) + 0.5            # U(0.5, 1.5)
+        return torch.rand(ws.shape, generator=g, device=device) + 0.5            # U(0.5, 1.5)
     if ws.init == "zeros":
         return torch.zeros(ws.shape)
-    return torch.randn(ws.shape, generator=g) * std
+    return torch.randn(ws.shape, generator=g, device=device) * std
 
 
 def write_random_model(config: dict, out_dir: str, seed: int = 0, std: float = 0.02,
-                       norm_init: str = "uniform", store_dtype: str = "bfloat16") -> str:
-    """config: the config.json dict of a registered architecture."""
+                       norm_init: str = "uniform", store_dtype: str = "bfloat16", device="cpu") -> str:
+    """config: the config.json dict of a registered architecture.  device: where the values are drawn; the
+    default (the CPU) gives the same folder on every machine, a GPU writes a many-gigabyte folder in seconds
+    (its values differ from the CPU's for the same seed)."""
     arch = resolve(config)
     cfg = arch.config_class.from_dict(config)
     model = DecoderModel(arch.build_spec(cfg))
@@ -49,7 +51,7 @@ def write_random_model(config: dict, out_dir: str, seed: int = 0, std: float = 0
         seen.add(name)
         store = torch.int32 if ws.kind == "table" else dtype
         items.append((name, tuple(ws.shape), store,
-                      lambda ws=ws, index=index, store=store: _draw(ws, seed, index, std, norm_init).to(store)))
+                      lambda ws=ws, index=index, store=store: _draw(ws, seed, index, std, norm_init, device).to(store).cpu()))
     write_safetensors(os.path.join(out_dir, "model.safetensors"), items)
     return out_dir
 

@@ -32,7 +32,7 @@ TINY_A = {
 TINY_B = {
     "architectures": ["Qwen3ForCausalLM"], "hidden_size": 96, "num_hidden_layers": 3,
     "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 32, "intermediate_size": 224,
-    "vocab_size": 517, "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"},
+    "vocab_size": 512, "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"},
     "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 1024,
 }
 # A third one with a window on some layers (two cache groups), odd sizes, one kv head.
@@ -50,7 +50,16 @@ TINY_F = {
     "vocab_size": 333, "rope_theta": 300000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 2048,
 }
-TINY = {"F": (TINY_F, dict(seed=4, std=0.06), 16), "A": (TINY_A, dict(seed=0, std=0.02), 8), "B": (TINY_B, dict(seed=1, std=0.05), 4),
+# A fifth one: windowed layers whose head size (64), page size (16) and group of 3 reach the tensor-core attention
+# kernels through the cache manager, with a window (40) that ends inside a 64-key tile and pages that are given back.
+TINY_V = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 192, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 264,
+    "vocab_size": 411, "rope_theta": 20000.0, "rms_norm_eps": 4e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 2048, "use_sliding_window": True, "sliding_window": 40,
+    "layer_types": ["sliding_attention", "full_attention"],
+}
+TINY = {"V": (TINY_V, dict(seed=5, std=0.07), 16), "F": (TINY_F, dict(seed=4, std=0.06), 16), "A": (TINY_A, dict(seed=0, std=0.02), 8), "B": (TINY_B, dict(seed=1, std=0.05), 4),
         "W": (TINY_W, dict(seed=2, std=0.08), 4)}
 
 

@@ -69,14 +69,23 @@ def check_cuts(runner, model_dir, vocab, tol, n=45, seed=5):
     assert runner.cache.free_pages() == pool
 
 
-def check_mixed(make, model_dir, vocab, page, tol, lens=(23, 9, 31, 17, 40, 12, 27), seed=7):
-    """Up to four live requests, portions of some beside decoded tokens of others, a pool so
-    small that pages are used again."""
+def check_mixed(make, model_dir, vocab, page, tol, lens=(23, 9, 31, 17, 40, 12, 27, 36, 20, 33, 14, 38), seed=7):
+    """Up to four live requests, portions of some beside decoded tokens of others, in a pool so small that pages are
+    used again: it holds four of the longest requests and not a page more, so every page that a finished request gives
+    back is handed out again (the pool is first in, first out).  The re-use is counted, not assumed."""
     rng = random.Random(seed)
     reqs = {f"r{i}": random_tokens(vocab, n, seed=100 + i) for i, n in enumerate(lens)}
     want = {k: plain_logits(model_dir, v) for k, v in reqs.items()}
-    pool_tokens = 4 * 48
-    runner = make(pool_tokens // page)
+    pages = 4 * -(-max(lens) // page)
+    runner = make(pages)
+    takes = {}                                             # page id -> how often it was handed out
+    for g in runner.cache.kv_groups:
+        inner = g.pool.take
+        def counted(inner=inner, gi=id(g)):
+            pg = inner()
+            takes[(gi, pg)] = takes.get((gi, pg), 0) + 1
+            return pg
+        g.pool.take = counted
     pending = list(reqs)
     live, got = {}, {k: [] for k in reqs}
     while pending or live:
@@ -107,4 +116,6 @@ def check_mixed(make, model_dir, vocab, page, tol, lens=(23, 9, 31, 17, 40, 12, 
     for k in reqs:
         e = rel_err(torch.cat(got[k]), want[k])
         assert e < tol, (k, e)
-    assert runner.cache.free_pages() == pool_tokens // page
+    assert runner.cache.free_pages() == pages
+    total, again = sum(takes.values()), sum(n - 1 for n in takes.values())
+    assert again * 3 >= total, f"only {again} of {total} page takes were of a page used before"

@@ -11,6 +11,9 @@ class TorchRefOps:
     prefill_tile = 64
 
     # ---------------------------------------------------------------- elementwise / norms
+    def scatter_i32(self, table, idx, val):
+        table[idx.long()] = val
+
     def embedding(self, ids, table):
         return table[ids.long()]
 
@@ -81,10 +84,12 @@ class TorchRefOps:
         q_start = meta.seg_q_start.tolist()
         pos0, kv_len = meta.seg_pos0.tolist(), meta.seg_kv_len.tolist()
         ps = meta.page_size
+        rows = getattr(meta, "table_rows", None)
+        rows = list(range(len(pos0))) if rows is None else rows.tolist()
         for s in range(len(pos0)):
             a, b, L = q_start[s], q_start[s + 1], kv_len[s]
             j = torch.arange(L, device=q.device)
-            pages = meta.block_table[s, j // ps].long()
+            pages = meta.block_table[rows[s], j // ps].long()
             k = k_cache[pages, :, j % ps, :].float()              # [L, KV, D]
             v = v_cache[pages, :, j % ps, :].float()
             k = k.repeat_interleave(H // KV, dim=1)

@@ -9,13 +9,13 @@ from tests.ref_ops import TorchRefOps
 TOL = 2e-5
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "V"])
 def test_whole_decode_and_portions(tiny_dirs, name):
     d, cfg, page = tiny_dirs[name]
     check_cuts(make_engine(d, page, 64, ops=TorchRefOps()), d, cfg["vocab_size"], TOL)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "V"])
 def test_mixed_batches_reuse_pages(tiny_dirs, name):
     d, cfg, page = tiny_dirs[name]
     check_mixed(lambda pages: make_engine(d, page, pages, ops=TorchRefOps()), d, cfg["vocab_size"], page, TOL)

@@ -212,22 +212,32 @@ def test_gemm_tc_swiglu(ops, M, inter, K):
     close(got, ref.swiglu(ref.linear(x, w)), torch.bfloat16)
 
 
-def make_meta(page_size, segs, num_pages, seed, tile=64):
-    """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns a meta object
-    shaped like engine.batch.GroupMeta."""
+def make_meta(page_size, segs, num_pages, seed, tile=64, indirect=False, window=None):
+    """segs: list of (pos0, n).  Builds block tables with shuffled pages; returns an object with the arrays the
+    engine's group view gives a mixer.  indirect: the table has more rows than entries, in another order, and
+    table_rows says which row an entry reads (the engine's device-resident tables); otherwise entry i reads row i.
+    window: pages that lie wholly before the window of an entry's FIRST fed position hold the null page, as after
+    the cache manager has given them back."""
     rng = np.random.default_rng(seed)
     free = list(rng.permutation(np.arange(1, num_pages + 1)))
     S = len(segs)
     kv_len = [p + n for p, n in segs]
     max_pages = max(-(-L // page_size) for L in kv_len)
-    table = np.zeros((S, max_pages), dtype=np.int32)
+    rows = list(range(S))
+    R = S
+    if indirect:
+        R = S + 3
+        rows = [int(r) for r in rng.permutation(np.arange(1, R))[:S]]
+    table = np.zeros((R, max_pages), dtype=np.int32)
     for s, L in enumerate(kv_len):
+        first_live = 0 if window is None else max(0, segs[s][0] - window + 1) // page_size
         for i in range(-(-L // page_size)):
-            table[s, i] = free.pop()
+            page = free.pop()
+            table[rows[s], i] = page if i >= first_live else 0
     q_start = np.zeros(S + 1, dtype=np.int32)
     q_start[1:] = np.cumsum([n for _, n in segs])
     positions = np.concatenate([np.arange(p, p + n) for p, n in segs]).astype(np.int32)
-    slots = np.concatenate([table[s, np.arange(p, p + n) // page_size] * page_size + np.arange(p, p + n) % page_size
+    slots = np.concatenate([table[rows[s], np.arange(p, p + n) // page_size] * page_size + np.arange(p, p + n) % page_size
                             for s, (p, n) in enumerate(segs)]).astype(np.int32)
     decode = [s for s, (_, n) in enumerate(segs) if n == 1]
     tiles = [(s, r) for s, (_, n) in enumerate(segs) if n > 1 for r in range(0, n, tile)]
@@ -235,10 +245,10 @@ def make_meta(page_size, segs, num_pages, seed, tile=64):
     t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
     return types.SimpleNamespace(
         page_size=page_size, tile=tile, positions=t(positions), slots=t(slots), block_table=t(table),
+        table_rows=t(rows) if indirect else None, rows=rows,
         max_pages=max_pages, seg_q_start=t(q_start), seg_pos0=t([p for p, _ in segs]), seg_kv_len=t(kv_len),
         decode_segs=t(decode), prefill_tiles=t(tiles).view(-1, 2), prefill_tiles2=t(tiles2).view(-1, 2),
-        num_prefill_tiles2=len(tiles2), num_decode=len(decode),
-        num_prefill_tiles=len(tiles), max_kv_len=max(kv_len), num_tokens=int(q_start[-1]))
+        max_kv_len=max(kv_len), num_tokens=int(q_start[-1]))
 
 
 ATTN_SHAPES = [  # H, KV, D, page
@@ -276,16 +286,21 @@ def test_qk_norm_rope_cache(ops, dtype, H, KV, D, page):
 def test_paged_attention(ops, dtype, H, KV, D, page, window):
     g = torch.Generator().manual_seed(6)
     segs = [(0, 70), (150, 1), (31, 1), (40, 29), (0, 1), (299, 1), (3, 2)]
-    meta = make_meta(page, segs, 200, seed=2)
+    # rows of a larger table in another order, and (with a window) null entries where pages were given back
+    meta = make_meta(page, segs, 200, seed=2, indirect=True, window=window)
     T = meta.num_tokens
     q = torch.randn(T, H * D, generator=g).to(dtype).to(DEV)
     kc = torch.randn(201, KV, page, D, generator=g).to(dtype).to(DEV)
     vc = torch.randn(201, KV, page, D, generator=g).to(dtype).to(DEV)
     # make one far key of the long decode stand out, so that a lost or misplaced key shows
-    kc[meta.block_table[5, 2].long(), :, 3, :] *= 4.0
+    far = 2 * page + 3 if window is None else 299 - 7             # (inside the window when there is one)
+    kc[meta.block_table[meta.rows[5], far // page].long(), :, far % page, :] *= 4.0
+    kc[0], vc[0] = 1e4, 1e4                                       # the null page: reading it as a key would show
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
-    # splits merged by a cluster through shared memory / by the last block to finish / by a merge kernel / generic kernels
-    for fast, fused, cluster in ((True, True, True), (True, True, False), (True, False, False), (False, False, False)):
+    # splits merged by a cluster through shared memory / by the last block to finish / by a merge kernel (also when the
+    # cluster switch is on) / generic kernels
+    for fast, fused, cluster in ((True, True, True), (True, True, False), (True, False, False), (True, False, True),
+                                 (False, False, False)):
         for splits in (None, 1, 3):
             ops.force_splits, ops.fast_attention, ops.fused_merge, ops.cluster_merge = splits, fast, fused, cluster
             ops.tc_attention = splits != 3               # prompt portions: tcgen05 kernel, and the mma.sync kernel
@@ -307,11 +322,12 @@ def test_prefill_attention_long(ops, H, KV, D, page, window):
     """Portions of hundreds of rows with offsets: whole tiles, diagonal tiles, a far key that stands out."""
     g = torch.Generator().manual_seed(9)
     segs = [(0, 300), (517, 260), (64, 129), (1000, 2)]
-    meta = make_meta(page, segs, 400, seed=3)
+    meta = make_meta(page, segs, 400, seed=3, indirect=True, window=window)
     q = torch.randn(meta.num_tokens, H * D, generator=g).to(torch.bfloat16).to(DEV)
     kc = torch.randn(401, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
     vc = torch.randn(401, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
-    kc[meta.block_table[1, 3].long(), :, 5, :] *= 3.0
+    far = 3 * page + 5 if window is None else 517 - 150
+    kc[meta.block_table[meta.rows[1], far // page].long(), :, far % page, :] *= 3.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
     for tc in (True, False):
         ops.tc_attention = tc
@@ -371,55 +387,6 @@ def test_sampling_distribution(ops):
     assert (freq - probs).abs().max() < 0.03
 
 
-@pytest.fixture
-def chain_ops(ops):
-    """The kernel namespace with the optional fused block-tail kernel switched on (it is off by default)."""
-    ops.decode_chain_on = True
-    yield ops
-    ops.decode_chain_on = False
-
-
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("hidden,q_dim,inter", [(192, 128, 320), (2560, 4096, 9728), (640, 448, 1088), (1024, 2048, 3072)])
-def test_decode_chain(chain_ops, M, hidden, q_dim, inter):
-    """Out-projection + residual + norm + gated feed-forward as one persistent kernel against the separate kernels
-    (same rounding points: equal up to the order of float32 sums) and against float32 arithmetic."""
-    ops = chain_ops
-    g = torch.Generator().manual_seed(M * 1000 + hidden)
-    mk = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(torch.bfloat16).to(DEV)
-    attn, x = mk(M, q_dim), mk(M, hidden, scale=2.0)
-    w_o, w_gu, w_d = mk(hidden, q_dim, scale=q_dim ** -0.5), mk(2 * inter, hidden, scale=hidden ** -0.5), mk(hidden, inter, scale=inter ** -0.5)
-    norm_w = (torch.rand(hidden, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
-    eps = 1e-5
-    ref = TorchRefOps()
-    x_ref = x.clone()
-    h = ref.add_rmsnorm(x_ref, ref.linear(attn, w_o), norm_w, eps)
-    want = ref.linear(ref.swiglu(ref.linear(h, w_gu)), w_d)
-    for rep in range(3):                               # the kernel leaves its counters ready for the next call
-        x_own = x.clone()
-        got = ops.decode_chain(attn, w_o, x_own, norm_w, eps, w_gu, w_d)
-        assert got is not None, "sizes that the fused kernel must take"
-        ops.check_errors()
-        close(x_own, x_ref, torch.bfloat16)
-        close(got, want, torch.bfloat16)
-    # a strided view of the attention output (rows of a wider buffer) gives the same result
-    wide = torch.zeros(M, q_dim + 64, dtype=torch.bfloat16, device=DEV)
-    wide[:, :q_dim] = attn
-    x2 = x.clone()
-    got2 = ops.decode_chain(wide[:, :q_dim], w_o, x2, norm_w, eps, w_gu, w_d)
-    ops.check_errors()
-    assert torch.equal(got2, got) and torch.equal(x2, x_own)
-
-
-def test_decode_chain_refuses(chain_ops):
-    ops = chain_ops
-    mk = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=DEV)
-    # 17 rows, a width that is no multiple of 64, float32 rows: the caller is told to use the separate kernels
-    assert ops.decode_chain(mk(17, 128), mk(192, 128), mk(17, 192), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
-    assert ops.decode_chain(mk(4, 128), mk(200, 128), mk(4, 200), mk(200), 1e-5, mk(640, 200), mk(200, 320)) is None
-    assert ops.decode_chain(mk(4, 128), mk(192, 128), mk(4, 192).float(), mk(192), 1e-5, mk(640, 192), mk(192, 320)) is None
-
-
 @pytest.mark.parametrize("M", [1, 5, 8, 13, 32])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (2560, 9728), (100, 64), (516, 192), (19456, 2560)])
 def test_deferred_sums(ops, M, N, K):
@@ -463,46 +430,6 @@ def test_deferred_sums(ops, M, N, K):
         ops._linear_choice = saved
 
 
-@pytest.mark.parametrize("H,KV,D,page", [(32, 8, 128, 16), (8, 8, 64, 16), (12, 1, 128, 32), (16, 1, 64, 16), (4, 4, 64, 32),
-                                         (6, 2, 128, 16)])
-@pytest.mark.parametrize("window", [None, 29])
-def test_decode_attention_with_fused_qk(ops, H, KV, D, page, window):
-    """Only decoded tokens in the step: q/k norm, rotation and the cache write inside the attention kernel give the
-    same rows and the same cache as the separate kernel (new tokens at a page's first and last place, first tokens of
-    a request, several splits)."""
-    g = torch.Generator().manual_seed(13)
-    segs = [(150, 1), (31, 1), (0, 1), (299, 1), (page - 1, 1), (page, 1), (16, 1), (15, 1), (63, 1)]
-    meta = make_meta(page, segs, 200, seed=4)
-    T = meta.num_tokens
-    qkv = torch.randn(T, (H + 2 * KV) * D, generator=g).to(torch.bfloat16).to(DEV)
-    qw = (torch.rand(D, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
-    kw = (torch.rand(D, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
-    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(DEV)
-    kc0 = torch.randn(201, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
-    vc0 = torch.randn(201, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
-    for use_norm, use_rope, owns in ((True, True, True), (False, True, True), (True, False, True), (True, True, False)):
-        a = (qw, kw) if use_norm else (None, None)
-        f = inv_freq if use_rope else None
-        for splits in (None, 1, 3):
-            res = []
-            for fuse in (False, True):
-                kc, vc = kc0.clone(), vc0.clone()
-                saved = ops.fuse_qk
-                ops.fuse_qk, ops.force_splits = fuse, splits
-                before = ops.launches
-                try:
-                    out = ops.qk_attention(qkv.clone(), H, KV, D, *a, 1e-6, f, meta, kc, vc, owns, D ** -0.5, window)
-                finally:
-                    ops.fuse_qk, ops.force_splits = saved, None
-                res.append((out, kc, vc, ops.launches - before))
-                ops.check_errors()
-            (o1, k1, v1, n1), (o2, k2, v2, n2) = res
-            assert n2 == n1 - 1                            # one launch less
-            assert torch.equal(k1, k2) and torch.equal(v1, v2)
-            close(o2, o1, torch.bfloat16, scale=o1.float().abs().max())
-            assert (o2.float() - o1.float()).abs().max() <= 2e-2 * o1.float().abs().max()
-
-
 @pytest.mark.parametrize("H,KV,D,page", [(32, 8, 128, 16), (8, 2, 64, 64), (16, 1, 128, 256)])
 @pytest.mark.parametrize("window", [None, 1000])
 def test_decode_attention_long_context(ops, H, KV, D, page, window):
@@ -511,13 +438,13 @@ def test_decode_attention_long_context(ops, H, KV, D, page, window):
     g = torch.Generator().manual_seed(21)
     segs = [(4099, 1), (8999, 1), (17, 1), (1023, 1), (1024, 1), (0, 1)]
     pages = sum((p + 1 + page - 1) // page for p, _ in segs) + 2
-    meta = make_meta(page, segs, pages, seed=6)
+    meta = make_meta(page, segs, pages, seed=6, indirect=True, window=window)
     T = meta.num_tokens
     q = torch.randn(T, H * D, generator=g).to(torch.bfloat16).to(DEV)
     kc = torch.randn(pages + 1, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
     vc = torch.randn(pages + 1, KV, page, D, generator=g).to(torch.bfloat16).to(DEV)
     far = 5000 if window is None else 8999 - 700
-    kc[meta.block_table[1, far // page].long(), :, far % page, :] *= 4.0
+    kc[meta.block_table[meta.rows[1], far // page].long(), :, far % page, :] *= 4.0
     want = TorchRefOps().paged_attention(q, kc, vc, meta, H, KV, D, D ** -0.5, window)
     for bulk, cluster in ((True, True), (True, False), (False, False)):
         for splits in (None, 5, 8, 11):

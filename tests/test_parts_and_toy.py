@@ -7,10 +7,10 @@ import torch
 
 from mini_inference_b200.cache import CacheManager
 from mini_inference_b200.config.spec import ExecStep, LayerSpec, ModelSpec, PartSpec
-from mini_inference_b200.engine.batch import StepBatch, StepEntry
+from mini_inference_b200.engine.batch import BatchBuilder, StepEntry
 from mini_inference_b200.engine.runner import ModelRunner
 from mini_inference_b200.parts import (DecoderModel, KVCacheNeed, Part, StateNeed, StepContext, WeightSpec, build_part,
-                                       register_mixer)
+                                       register_block, register_mixer)
 from tests.helpers import random_cuts, rel_err
 from tests.plain import qwen3_plain as plain
 from tests.ref_ops import TorchRefOps
@@ -29,7 +29,10 @@ def get_ops(device):
 @register_mixer("toy_ema")
 class ToyEMA(Part):
     """y_t = W s_t with s_t = a * s_{t-1} + (1 - a) * h_t: a running average kept per request
-    in a state slot, advanced token by token in position order."""
+    in a state slot, advanced token by token in position order.  It asks the step builder for a per-entry array of
+    its own (the flat row behind each entry's last token), which reaches it on the device beside the built-in fields."""
+    step_arrays_key = "toy_ema"
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden, self.decay = spec.get("hidden_size"), spec.get("decay")
@@ -43,12 +46,19 @@ class ToyEMA(Part):
     def load(self, tensors, dtype, device):
         self.mix = tensors["mix"]
 
+    def step_arrays(self, facts):
+        return {"seg_end": facts.q_start[1:].copy()}
+
     def forward(self, h, ctx, cache, position, owns_cache=True):
         out = torch.empty_like(h)
         q = ctx.batch.host["seg_q_start"]
+        ends = ctx.batch.extras["toy_ema"]["seg_end"]                  # the array this mixer asked for, on the device
+        assert ends.device == h.device and ends.dtype == torch.int32
+        assert ends.tolist() == list(ctx.batch.extras_host["toy_ema"]["seg_end"]) == [int(v) for v in q[1:]]
+        ends = ends.tolist()
         for s, slot in enumerate(ctx.batch.host["seg_slot"]):
             state = cache.state[slot]
-            for t in range(q[s], q[s + 1]):
+            for t in range(q[s], ends[s]):
                 state.mul_(self.decay).add_(h[t].float(), alpha=1 - self.decay)
                 out[t] = state.to(h.dtype)
         return ctx.ops.linear(out, self.mix)
@@ -71,9 +81,11 @@ def toy_spec(hidden=64, vocab=97):
         d.update({f"mixer.{t}": p + t for t in mixer_tensors})
         return tuple(sorted(d.items()))
     qkvo = ["q_proj", "k_proj", "v_proj", "o_proj"]
-    layers = (LayerSpec("prenorm", attn, ffn, norm, pos, names(0, qkvo + ["q_norm", "k_norm"])),
-              LayerSpec("prenorm", toy, ffn, norm, PartSpec.of("none"), names(1, ["mix"])),
-              LayerSpec("prenorm", win, ffn, norm, pos, names(2, qkvo)))
+    def layer(mixer, position, weight_names):
+        return LayerSpec.of("prenorm", weight_names, mixer=mixer, feed_forward=ffn, norm1=norm, norm2=norm, position=position)
+    layers = (layer(attn, pos, names(0, qkvo + ["q_norm", "k_norm"])),
+              layer(toy, PartSpec.of("none"), names(1, ["mix"])),
+              layer(win, pos, names(2, qkvo)))
     # layer 0 runs twice (own caches); the last step re-reads the keys and values of step 0
     order = (ExecStep(0), ExecStep(1), ExecStep(2), ExecStep(0), ExecStep(0, cache_from=0))
     return ModelSpec(hidden_size=hidden, vocab_size=vocab, layers=layers, order=order, final_norm=norm,
@@ -143,6 +155,7 @@ def test_toy_mixer_is_registered_built_and_stepped(device):
     cache = CacheManager(needs, 4, 64, 4, 512, dtype=torch.float32, device=device)
     assert len(cache.kv_groups) == 2 and len(cache.state_groups) == 1        # full keys (2 steps) and a window
     runner = ModelRunner(model, cache, get_ops(device))
+    assert set(runner.builder.hooks) == {"paged_attention", "toy_ema"}      # one hook per kind of part, not per layer
     g = torch.Generator().manual_seed(3)
     seqs = {k: torch.randint(0, 97, (n,), generator=g).tolist() for k, n in (("a", 29), ("b", 17))}
     want = {k: toy_plain(w, ids) for k, ids in seqs.items()}
@@ -169,13 +182,15 @@ def test_toy_mixer_is_registered_built_and_stepped(device):
 
 
 # ---------------------------------------------------------------- each built-in part alone
-def ctx_for(device, entries_lens, cache, dtype=torch.float32):
+def ctx_for(device, entries_lens, cache, dtype=torch.float32, part=None):
     seqs = [cache.admit(i) for i in range(len(entries_lens))]
     entries = []
     for s, n in zip(seqs, entries_lens):
         cache.ensure(s, n)
         entries.append(StepEntry(s, [1] * n, []))
-    batch = StepBatch(entries, cache, device)
+    hooks = {part.step_arrays_key: part.step_arrays} if part is not None else {}
+    batch = BatchBuilder(cache, device, hooks).build(entries)
+    batch.apply_table_updates(get_ops(device))
     return StepContext(get_ops(device), batch, dtype, device), seqs
 
 
@@ -233,7 +248,7 @@ def test_attention_part(device, window, qk_norm):
     part.load({k: v.to(device) for k, v in w.items()}, torch.float32, device)
     cache = CacheManager([part.cache_need()], 4, 32, 2, 256, dtype=torch.float32, device=device)
     lens = [19, 11]
-    ctx, seqs = ctx_for(device, lens, cache)
+    ctx, seqs = ctx_for(device, lens, cache, part=part)
     h = torch.randn(sum(lens), hid, generator=g)
     y = part.forward(h.to(device), ctx, cache.layer_caches[0], pos).cpu()
     at = 0
@@ -318,9 +333,11 @@ def routed_spec(hidden=48, vocab=61, inter=40, experts=4):
         d.update({f"mixer.{t}": p + t for t in ("q_proj", "k_proj", "v_proj", "o_proj")})
         d.update({f"feed_forward.{t}": p + t for t in ffn_tensors})
         return tuple(sorted(d.items()))
-    layers = (LayerSpec("prenorm", attn, routed, norm, pos, names(0, ["router", "w_in", "w_out", "place"])),
-              LayerSpec("prenorm", attn, dense, norm, pos, names(1, ["gate_proj", "up_proj", "down_proj"])),
-              LayerSpec("prenorm", attn, routed, norm, pos, names(2, ["router", "w_in", "w_out", "place"])))
+    def layer(ffn, weight_names):
+        return LayerSpec.of("prenorm", weight_names, mixer=attn, feed_forward=ffn, norm1=norm, norm2=norm, position=pos)
+    layers = (layer(routed, names(0, ["router", "w_in", "w_out", "place"])),
+              layer(dense, names(1, ["gate_proj", "up_proj", "down_proj"])),
+              layer(routed, names(2, ["router", "w_in", "w_out", "place"])))
     return ModelSpec(hidden_size=hidden, vocab_size=vocab, layers=layers, order=tuple(ExecStep(i) for i in range(3)),
                      final_norm=norm, embedding_name="emb", final_norm_name="fn", lm_head_name=None, max_position=128)
 
@@ -384,3 +401,82 @@ def test_toy_routed_feed_forward_and_learned_position(device):
         cache.free(seq)
         assert rel_err(torch.cat(out), want) < 3e-5, cuts
     cache.check_invariants()
+
+
+# ---------------------------------------------------------------- a toy arrangement with roles of its own
+@register_block("toy_parallel")
+class ToyParallelBlock(Part):
+    """x = x + mixer(n(x)) + feed_forward(n(x)) with ONE norm n shared by both branches, and a second norm of another
+    size-less kind ("post") applied to the feed-forward's output: an arrangement whose roles are not the pre-norm block's."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "norm": "norm", "post": "norm", "position": "position"}
+
+    def __init__(self, spec, parts):
+        super().__init__(spec)
+        self.parts = dict(parts)
+        self.mixer = parts["mixer"]
+
+    def forward(self, x, delta, ctx, cache, owns_cache=True):
+        p = self.parts
+        h = p["norm"].forward(x, delta, ctx)
+        a = p["mixer"].forward(h, ctx, cache, p["position"], owns_cache)
+        f = p["feed_forward"].forward(h, ctx)
+        rows = torch.arange(f.shape[0], dtype=torch.int32, device=f.device)
+        f = p["post"].forward(f, None, ctx, rows=rows)
+        return x, (a.float() + f.float()).to(x.dtype)
+
+
+def test_a_block_names_its_own_roles():
+    """The layer description is a mapping role -> part that the block interprets: a block with one shared norm and a
+    post-norm is built and stepped without touching the framework; a layer that gives the wrong roles is refused."""
+    hidden = 48
+    norm = PartSpec.of("rmsnorm", size=hidden, eps=1e-5)
+    attn = PartSpec.of("gqa_attention", hidden_size=hidden, num_heads=3, num_kv_heads=1, head_dim=16, scale=0.25,
+                       qk_norm=False, window=None)
+    ffn = PartSpec.of("swiglu", hidden_size=hidden, intermediate_size=40)
+    pos = PartSpec.of("rotary", head_dim=16, theta=10000.0)
+    names = {"norm.weight": "n", "post.weight": "pn", "mixer.q_proj": "q", "mixer.k_proj": "k", "mixer.v_proj": "v",
+             "mixer.o_proj": "o", "feed_forward.gate_proj": "g", "feed_forward.up_proj": "u", "feed_forward.down_proj": "d"}
+    layer = LayerSpec.of("toy_parallel", names, mixer=attn, feed_forward=ffn, norm=norm, post=norm, position=pos)
+    spec = ModelSpec(hidden_size=hidden, vocab_size=53, layers=(layer,), order=(ExecStep(0), ExecStep(0)), final_norm=norm,
+                     embedding_name="emb", final_norm_name="fn", lm_head_name=None, max_position=64)
+    model = DecoderModel(spec)
+    assert {n for n, _ in model.weight_table()} == {"emb", "fn", *names.values()}
+    w = random_weights(model, torch.float32, "cpu", seed=4)
+    cache = CacheManager(model.cache_needs(), 4, 32, 2, 64, dtype=torch.float32, device="cpu")
+    runner = ModelRunner(model, cache, TorchRefOps())
+    ids = [5, 9, 2, 44, 17, 30, 8, 8, 21]
+    n = len(ids)
+    x = plain.embed(ids, w["emb"])
+    cos, sin = plain.rotary_tables(torch.arange(n), 16, 10000.0, x.dtype)
+    for _ in range(2):
+        h = plain.rms_norm(x, w["n"], 1e-5)
+        q = plain.apply_rope((h @ w["q"].T).view(n, 3, 16), cos, sin)
+        k = plain.apply_rope((h @ w["k"].T).view(n, 1, 16), cos, sin)
+        a = plain.causal_attention(q, k, (h @ w["v"].T).view(n, 1, 16), 0.25, None).reshape(n, hidden) @ w["o"].T
+        f = (torch.nn.functional.silu(h @ w["g"].T) * (h @ w["u"].T)) @ w["d"].T
+        x = x + a + plain.rms_norm(f, w["pn"], 1e-5)
+    want = plain.rms_norm(x, w["fn"], 1e-5) @ w["emb"].T
+    seq, out = cache.admit("p"), []
+    for a0, b0 in ((0, 4), (4, 6), (6, 9)):
+        out.append(runner.step([StepEntry(seq, ids[a0:b0], range(b0 - a0))]))
+    assert rel_err(torch.cat(out), want) < 3e-5
+    with pytest.raises(KeyError, match="roles"):
+        DecoderModel(ModelSpec(hidden_size=hidden, vocab_size=53, order=(ExecStep(0),), final_norm=norm, embedding_name="emb",
+                               final_norm_name="fn", lm_head_name=None, max_position=64,
+                               layers=(LayerSpec.of("prenorm", names, mixer=attn, feed_forward=ffn, norm=norm, position=pos),)))
+
+
+def test_optional_protocol_is_declared_not_probed():
+    """Every optional fast-path name exists on Part with a default that means "not offered"; the built-in parts override
+    what they offer, and the pre-norm block finds the attention mixer's first weight (the qkv matrix) for its hint."""
+    base = Part(PartSpec.of("x"))
+    assert (base.offers_open, base.open_weight, base.first_weight, base.accepts_deferred, base.takes_next_weight,
+            base.step_arrays_key) == (False, None, None, False, False, None)
+    model = DecoderModel(toy_spec())
+    random_weights(model, torch.float32, "cpu")
+    block = model.blocks[0]
+    assert block.open_mixer and block.open_ffn and block.hint1 and block.hint2
+    assert block.mixer.first_weight is block.mixer.qkv and block.feed_forward.first_weight is block.feed_forward.gate_up
+    assert block.mixer.open_weight is block.mixer.o
+    assert not model.blocks[1].open_mixer                                  # the toy mixer offers nothing
+    assert model.deferrable_shapes() == {(64, 64), (64, 96)}

@@ -27,16 +27,23 @@ def problem(B, ctx_lens, H, KV, D, page, seed):
     return meta, q, kc, vc
 
 
-def call_noalloc(lib, q, kc, vc, meta, H, KV, D, splits, window=0):
+def call_noalloc(lib, q, kc, vc, meta, H, KV, D, splits, window=0, check_free=False):
+    """check_free: compare the DRIVER's free-memory figure around the call (it sees a cudaMalloc inside the library,
+    which the framework allocator's counters cannot); only meaningful once the library's kernels are loaded, so the
+    first call of a test runs without it."""
     out = torch.full((q.shape[0], H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
-    rc = lib.mi_attn_decode_noalloc(p(q), q.stride(0), p(kc), p(vc), p(out), p(meta.decode_segs), meta.num_decode,
+    free_before = torch.cuda.mem_get_info()[0]
+    rc = lib.mi_attn_decode_noalloc(p(q), q.stride(0), p(kc), p(vc), p(out), p(meta.decode_segs), meta.decode_segs.shape[0],
                                     p(meta.seg_q_start), p(meta.seg_kv_len), p(meta.block_table), meta.max_pages,
                                     H, KV, D, meta.page_size, splits, ctypes.c_float(D ** -0.5), window, stream)
     torch.cuda.synchronize()
     assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == before     # the call allocated nothing
+    if check_free:
+        assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated during the call"
     return rc, out
 
 
@@ -49,9 +56,9 @@ def test_no_alloc_decode_attention_matches_ordinary_entry_point():
     H, KV, D, page = 32, 8, 128, 16
     # two calls in a row: the second is smaller and uses fewer splits, so stale partials of the
     # first call lie in the array beside and behind what the second call writes
-    for lens, splits, seed in (([700, 33, 1, 260, 129], 5, 1), ([90, 517], 2, 2), ([300], 1, 3)):
+    for call, (lens, splits, seed) in enumerate((([700, 33, 1, 260, 129], 5, 1), ([90, 517], 2, 2), ([300], 1, 3))):
         meta, q, kc, vc = problem(len(lens), lens, H, KV, D, page, seed)
-        rc, got = call_noalloc(lib, q, kc, vc, meta, H, KV, D, splits)
+        rc, got = call_noalloc(lib, q, kc, vc, meta, H, KV, D, splits, check_free=call > 0)
         assert rc == 0, lib.mi_attn_decode_noalloc_strerror(rc).decode()
         ops.force_splits = splits
         try:
