@@ -12,7 +12,9 @@ weights, bfloat16.  Prints ONE JSON line:
   prefill      one 2,048-token prompt: tokens/s, ms, and flops / time / measured bf16 peak
   roofline     the decode step's bytes (every weight once + the cache of the live requests)
                / its time, against the measured copy bandwidth
-  points       decode tokens/s at batch 1 and 64
+  points       decode tokens/s at batch 1 and 64 (context 4,096), and BASELINE's workload (512-token prompts + 256
+               greedy tokens through the scheduler) at batch 1, 8 and 64
+  check        logits of decode steps in the timed configuration against a float32 engine with the same weights
 The weights (8 GB) and the cache are far larger than the 126 MB L2, so nothing is flushed
 between steps.  More than one GPU is outside this engine: --gpus N>1 says so and exits 2.
 """
@@ -162,8 +164,7 @@ def decode_e2e(llm, torch, batch, ctx, steps, warmup, vocab):
     dt = time.perf_counter() - t0
     while llm.has_work():
         llm.step()
-    B = llm.graphs.bucket_for(batch)
-    return {"tok_s": batch * steps / dt, "h2d": llm.graphs.batches[B].size * 4, "d2h": 4 * batch}
+    return {"tok_s": batch * steps / dt, "h2d": llm.graphs.last_h2d_bytes, "d2h": 4 * batch}
 
 
 def prefill(llm, torch, tokens, vocab, warmup=3, reps=3, pause=0.0):
@@ -190,61 +191,52 @@ def prefill(llm, torch, tokens, vocab, warmup=3, reps=3, pause=0.0):
     return min(times)
 
 
-def profile(args, cfg, torch, LLM):
-    """A small, bounded run for a profiler: no prefill before the decode steps (the cache holds
-    zeros at the benchmark's context length), one graph bucket, few launches.  The timed steps sit
-    between cudaProfilerStart and cudaProfilerStop (ncu --profile-from-start off captures only them)."""
-    from mini_inference_b200.engine.batch import StepEntry
-    from mini_inference_b200.engine.graphs import DecodeGraphs
-    vocab = cfg["vocab_size"]
-    llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=args.page_size,
-              kv_cache_tokens=args.batch * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=args.batch,
-              max_model_len=args.ctx, max_batched_tokens=4096, cuda_graphs=False)
-    if args.profile == "prefill":
-        prefill(llm, torch, 2048, vocab, warmup=0, reps=1)
-        torch.cuda.profiler.start()
-        ms = prefill(llm, torch, 2048, vocab, warmup=0, reps=args.steps)
-        torch.cuda.profiler.stop()
-        print(f"prefill 2048 tokens: {ms:.3f} ms")
-        return 0
-    # which kernel runs each product is timed at start-up; under a profiler those timings are distorted, so a
-    # plain run can save its table (--choices FILE) and the profiled run of the same command reads it back
-    if args.choices and os.path.isfile(args.choices):
-        with open(args.choices) as f:
-            llm.ops._linear_choice = {tuple(int(v) for v in k.split(",")): c for k, c in json.load(f).items()}
-    else:
-        llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32},
-                            deferrable=llm.model.deferrable_shapes())
-        if args.choices:
-            with open(args.choices, "w") as f:
-                json.dump({",".join(str(v) for v in k): c for k, c in llm.ops._linear_choice.items()}, f)
-    llm.graphs = DecodeGraphs(llm.runner, args.batch, buckets=[args.batch])
-    llm.graphs.capture()
-    seqs = []
-    for i in range(args.batch):
-        seq = llm.cache.admit(("p", i), args.ctx)
-        llm.cache.ensure(seq, args.ctx - args.steps - args.warmup - 1)
-        llm.cache.commit(seq, args.ctx - args.steps - args.warmup - 1)
-        seqs.append(seq)
-    G, B = llm.graphs, args.batch
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for i in range(args.warmup + args.steps):
-        if i == args.warmup:
-            torch.cuda.profiler.start()
-            start.record()
-        for s in seqs:
-            llm.cache.ensure(s, s.num_tokens + 1)
-        G.fill(B, seqs, [1] * B if i == 0 else None)
-        G.replay(B)
-        G.feed_back(B)
-        for s in seqs:
-            llm.cache.commit(s, s.num_tokens + 1)
-    stop.record()
+def generate_workload(llm, torch, batch, prompt_len, new_tokens, vocab):
+    """BASELINE's decode workload through the scheduler: `batch` concurrent requests, each a prompt_len-token random
+    prompt and new_tokens greedy tokens.  Decode rate = tokens delivered after the last request's first token / the
+    time from then to the end."""
+    from mini_inference_b200.engine.request import SamplingParams
+    g = torch.Generator().manual_seed(2000 + batch)
+    reqs = [llm.add_request(torch.randint(0, vocab, (prompt_len,), generator=g).tolist(),
+                            SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)) for _ in range(batch)]
+    while llm.has_work():
+        llm.step()
     torch.cuda.synchronize()
-    torch.cuda.profiler.stop()
-    print(f"decode b{B} ctx{args.ctx}: {start.elapsed_time(stop) / args.steps:.3f} ms/step, "
-          f"{G.launches[B]} own kernels per step")
-    return 0
+    assert all(r.error is None and len(r.output_ids) == new_tokens for r in reqs)
+    t0 = max(r.times.tokens[0] for r in reqs)
+    t1 = max(r.times.finished for r in reqs)
+    tokens = sum(sum(1 for t in r.times.tokens if t > t0) for r in reqs)
+    return tokens / (t1 - t0)
+
+
+def logit_check(llm, torch, LLM, cfg, vocab, prompt_len=512, steps=8):
+    """One request in the state the decode timing runs in (start-up choice of GEMM kernels, partial sums handed to the
+    norm kernels, weight prefetch hints, graph replay from a bucket) against a float32 engine holding the same weights:
+    relative error of the decode steps' logits, and how many of the float32 argmax tokens the bfloat16 path picks."""
+    from mini_inference_b200.engine.batch import StepEntry
+    g = torch.Generator().manual_seed(99)
+    ids = torch.randint(0, vocab, (prompt_len + steps,), generator=g).tolist()
+    G = llm.graphs
+    B = G.bucket_for(1)
+    seq = llm.cache.admit(("check", 0), prompt_len + steps + 1)
+    llm.runner.step([StepEntry(seq, ids[:prompt_len], [])])
+    got = []
+    for k in range(steps):
+        assert llm.cache.ensure(seq, seq.num_tokens + 1)
+        G.fill(B, [seq], [ids[prompt_len + k]])
+        G.replay(B)
+        got.append(G.logits_out[B][0].float().clone())
+        llm.cache.commit(seq, seq.num_tokens + 1)
+    llm.cache.free(seq)
+    got = torch.stack(got)
+    ref_llm = LLM(None, random_config=cfg, random_seed=0, dtype="float32", device="cuda:0", kv_block_size=16,
+                  kv_cache_tokens=2048, kv_watermark=0.0, max_num_seqs=1, max_model_len=2048, cuda_graphs=False,
+                  random_draw_dtype="bfloat16")
+    ref = ref_llm.score(ids)[prompt_len:].float()
+    del ref_llm
+    err = ((got - ref).abs().max() / ref.abs().max()).item()
+    agree = int((got.argmax(-1) == ref.argmax(-1)).sum())
+    return {"logit_rel_err_vs_fp32": round(err, 5), "argmax_agree": f"{agree}/{steps}", "rows": steps, "context": prompt_len}
 
 
 def reference_arm(args):
@@ -281,10 +273,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--choices", default=None, help="--profile decode: file to keep the start-up choice of GEMM kernels in")
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
-                    help="run only a few decode steps (cache filled without a prefill) or one prefill, for ncu")
+    ap.add_argument("--skip-check", action="store_true", help="leave out the logits check against the float32 path")
     args = ap.parse_args()
     if args.gpus > 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported (use --gpus 1)")
@@ -302,8 +291,6 @@ def main():
     pk = peaks()
     nums = model_numbers(cfg, args.layers)
     kv_tokens = max(64, args.batch) * args.ctx + 4096
-    if args.profile:
-        return profile(args, cfg, torch, LLM)
     llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
               kv_cache_tokens=kv_tokens, kv_watermark=0.0, max_num_seqs=max(64, args.batch), max_model_len=args.ctx,
               max_batched_tokens=4096, cuda_graphs=False)
@@ -322,6 +309,10 @@ def main():
             for b in (1, 64):
                 r = decode_device(llm, torch, b, args.ctx, max(16, args.steps // 4), args.warmup, vocab)
                 points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            # BASELINE.json's own decode workload: 512-token prompts + 256 greedy tokens, through the scheduler
+            for b in (1, 8, 64):
+                points[f"gen512_256_b{b}"] = round(generate_workload(llm, torch, b, 512, 256, vocab), 1)
+        check = None if args.skip_check else logit_check(llm, torch, LLM, cfg, vocab)
 
     step_bytes = nums["weight_bytes"] + args.batch * main_run["ctx"] * nums["kv_bytes_per_token"]
     achieved = step_bytes / (main_run["ms"] * 1e-3) / 1e9
@@ -349,6 +340,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "check": check,
     }
     print(json.dumps(out))
     return 0

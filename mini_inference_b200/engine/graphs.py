@@ -29,7 +29,8 @@ class DecodeGraphs:
         self.device = runner.device
         self.buckets = [b for b in (buckets or DEFAULT_BUCKETS) if b < max_batch] + [max_batch]
         self.max_batch = max_batch
-        self.batches, self.graphs, self.tokens_out, self.launches = {}, {}, {}, {}
+        self.batches, self.graphs, self.tokens_out, self.logits_out, self.launches = {}, {}, {}, {}, {}
+        self.last_h2d_bytes = 0
         self.out_host, self._out_turn = {}, {}
         self.replays = self.eager_steps = 0
         self.capture_s = 0.0
@@ -37,7 +38,7 @@ class DecodeGraphs:
     # ---------------------------------------------------------------- capture
     def _forward(self, batch):
         logits = self.runner.forward(batch)
-        return self.ops.sample(logits, batch.temps, batch.seeds, batch.counters)
+        return self.ops.sample(logits, batch.temps, batch.seeds, batch.counters), logits
 
     def capture(self):
         import time
@@ -58,10 +59,11 @@ class DecodeGraphs:
             graph = torch.cuda.CUDAGraph()
             before = self.ops.launches
             with torch.cuda.graph(graph, pool=pool):
-                out = self._forward(batch)
+                out, logits = self._forward(batch)
             self.launches[B] = self.ops.launches - before
             pool = pool or graph.pool()
             self.batches[B], self.graphs[B], self.tokens_out[B] = batch, graph, out
+            self.logits_out[B] = logits                          # float32 [B, vocab] of the last replay (valid until the next)
         torch.cuda.synchronize(self.device)
         self.capture_s = time.perf_counter() - t0
 
@@ -77,7 +79,8 @@ class DecodeGraphs:
         buffer and start its copy.  tokens=None keeps the token ids already on the device (the
         previous step's samples, see feed_back).  Returns the bytes copied."""
         sampling = None if temps is None else (temps, seeds, counters)
-        return self.builder.refill(self.batches[B], seqs, tokens, sampling)
+        self.last_h2d_bytes = self.builder.refill(self.batches[B], seqs, tokens, sampling)
+        return self.last_h2d_bytes
 
     def feed_back(self, B):
         """Next step's token ids = this step's samples, without leaving the device."""

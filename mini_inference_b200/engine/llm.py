@@ -25,9 +25,12 @@ from .scheduler import Scheduler, Span
 
 class LLM:
     def __init__(self, model_dir: Optional[str], args: Optional[EngineArgs] = None, ops=None,
-                 random_config: Optional[dict] = None, random_seed: int = 0, random_std: float = 0.02, **overrides):
+                 random_config: Optional[dict] = None, random_seed: int = 0, random_std: float = 0.02,
+                 random_draw_dtype: Optional[str] = None, **overrides):
         """model_dir: a folder with config.json and model.safetensors.  With model_dir=None and
-        random_config (a config.json dict) the weights are drawn on the device instead."""
+        random_config (a config.json dict) the weights are drawn on the device instead (random_draw_dtype: the type
+        they are drawn in before they are cast to the engine's, so that a float32 engine can hold exactly the values
+        of a bfloat16 one)."""
         args = args or EngineArgs()
         for k, v in overrides.items():
             if not hasattr(args, k):
@@ -45,7 +48,8 @@ class LLM:
             arch = resolve(random_config)
             self.config = arch.config_class.from_dict(random_config)
             self.model = DecoderModel(arch.build_spec(self.config))
-            self.load_info = init_random_on_device(self.model, DTYPES[args.dtype], args.device, random_seed, random_std)
+            self.load_info = init_random_on_device(self.model, DTYPES[args.dtype], args.device, random_seed, random_std,
+                                                   draw_dtype=DTYPES[random_draw_dtype] if random_draw_dtype else None)
         self.load_info["load_time_s"] = round(time.perf_counter() - t0, 3)
         self.model_dir = model_dir
         self.device, self.dtype = self.model.device, DTYPES[args.dtype]
@@ -72,6 +76,11 @@ class LLM:
         self._ahead = None               # (chunks, handle) of a decode step launched but not yet delivered
         # step wall time split by kind (engine/custom_engine.py:69,140-142)
         self.step_time = {"decode": [0, 0.0], "other": [0, 0.0]}
+        # what those steps had to move and to compute, by the byte model of profiling/analyze.py:111-117 in the reference:
+        # a decode step reads every weight once and the cache of its requests; a step with prompt tokens is counted in flops
+        self.step_work = {"decode_bytes": 0, "other_flops": 0}
+        self._weight_bytes = int(self.load_info.get("weight_bytes", 0))
+        self._kv_bytes_per_token = self.cache.bytes_per_token()
 
     # ---------------------------------------------------------------- setup
     def enable_cuda_graphs(self):
@@ -187,6 +196,13 @@ class LLM:
         kind = "decode" if all(e - s == 1 and s > 0 for _, s, e in chunks) else "other"
         self.step_time[kind][0] += 1
         self.step_time[kind][1] += (time.perf_counter() - start) * 1e3
+        if kind == "decode":
+            self.step_work["decode_bytes"] += self._weight_bytes + self._kv_bytes_per_token * sum(e for _, _, e in chunks)
+        else:
+            rows = sum(e - s for _, s, e in chunks)
+            pairs = sum((e - s) * (s + e + 1) // 2 for _, s, e in chunks)          # (query, visible key) pairs
+            heads = sum(1 for r, _, e in chunks if e == r.total_len)
+            self.step_work["other_flops"] += self.model.step_flops(rows, pairs, heads)
 
     def _abort(self, e):
         """Fail this batch, keep serving."""
@@ -283,7 +299,8 @@ class LLM:
         t = {"decode_steps_timed": self.step_time["decode"][0],
              "decode_step_ms_total": round(self.step_time["decode"][1], 3),
              "other_steps_timed": self.step_time["other"][0],
-             "other_step_ms_total": round(self.step_time["other"][1], 3)}
+             "other_step_ms_total": round(self.step_time["other"][1], 3),
+             "decode_bytes_total": self.step_work["decode_bytes"], "other_flops_total": self.step_work["other_flops"]}
         g = self.graphs.stats() if self.graphs is not None else {}
         return {**self.scheduler.stats(), **self.cache.stats(), **g, **t}
 

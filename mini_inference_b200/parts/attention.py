@@ -55,6 +55,9 @@ class GQAAttention(Part):
     def first_weight(self):
         return self.qkv
 
+    def step_flops(self, rows, pairs):
+        return 4 * self.H * self.D * pairs                 # q.k and p.v, a multiply and an add each
+
     def step_arrays(self, facts):
         """The attention kernels' work lists: the entries that feed one token (decode kernel), and for the longer
         entries one (entry, first row) pair per tile of query rows (prompt kernels; the tensor-core kernel takes

@@ -117,6 +117,11 @@ class Part:
     def step_arrays(self, facts):
         return {}
 
+    def step_flops(self, rows: int, pairs: int) -> int:
+        """Floating-point operations beyond the part's matrix products, for `rows` tokens that see `pairs`
+        (query, key) pairs (an attention mixer: scores and weighted sum)."""
+        return 0
+
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}

@@ -104,6 +104,17 @@ class DecoderModel:
                     shapes.add((w.shape[0], w.shape[1]))
         return frozenset(shapes)
 
+    def step_flops(self, rows: int, pairs: int, logit_rows: int) -> int:
+        """Floating-point operations of a step that feeds `rows` tokens which see `pairs` (query, key) pairs in all and
+        wants logits for `logit_rows` of them: 2 per weight element and row, plus what the mixers report."""
+        total = 2 * logit_rows * self.lm_head.numel()
+        for step in self.spec.order:
+            for part in self.blocks[step.layer].parts.values():
+                total += 2 * rows * sum(v.numel() for v in vars(part).values()
+                                        if isinstance(v, torch.Tensor) and v.dim() == 2 and v.is_floating_point())
+                total += part.step_flops(rows, pairs)
+        return total
+
     def step_array_hooks(self):
         """{key: part.step_arrays} of the parts that ask for per-step arrays of their own, one per key."""
         hooks = {}

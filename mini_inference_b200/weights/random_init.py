@@ -57,7 +57,7 @@ def write_random_model(config: dict, out_dir: str, seed: int = 0, std: float = 0
 
 
 def init_random_on_device(model, dtype: torch.dtype, device, seed: int = 0, std: float = 0.02,
-                          norm_init: str = "ones") -> dict:
+                          norm_init: str = "ones", draw_dtype: torch.dtype = None) -> dict:
     """Random weights drawn directly on the device, tensor by tensor (benchmarks of large
     configurations: no folder is written, nothing passes through host memory)."""
     g = torch.Generator(device=device).manual_seed(seed)
@@ -69,9 +69,9 @@ def init_random_on_device(model, dtype: torch.dtype, device, seed: int = 0, std:
             t = torch.zeros(ws.shape, dtype=torch.int32, device=device)
         elif ws.init == "norm":
             t = torch.ones(ws.shape, dtype=dtype, device=device) if norm_init == "ones" else \
-                (torch.rand(ws.shape, generator=g, device=device) + 0.5).to(dtype)
+                (torch.rand(ws.shape, generator=g, device=device) + 0.5).to(draw_dtype or dtype).to(dtype)
         else:
-            t = torch.empty(ws.shape, dtype=dtype, device=device).normal_(0.0, std, generator=g)
+            t = torch.empty(ws.shape, dtype=draw_dtype or dtype, device=device).normal_(0.0, std, generator=g).to(dtype)
         tensors[name] = t
         nbytes += t.numel() * t.element_size()
     model.load(tensors, dtype, device)

@@ -71,7 +71,8 @@ def open_model_tensors(model_dir: str) -> Dict[str, SafetensorsFile]:
         with open(index) as fh:
             weight_map = json.load(fh)["weight_map"]
         files = {fn: SafetensorsFile(os.path.join(model_dir, fn)) for fn in sorted(set(weight_map.values()))}
-        return {name: files[fn] for name, fn in weight_map.items()}
+        # a name the index sends to a shard that does not hold it counts as missing
+        return {name: files[fn] for name, fn in weight_map.items() if name in files[fn].header}
     raise FileNotFoundError(f"{model_dir} has neither model.safetensors nor model.safetensors.index.json")
 
 

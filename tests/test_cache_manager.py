@@ -125,3 +125,62 @@ def test_random_orders_keep_invariants(seed):
         m.free(s)
     m.check_invariants()
     assert m.free_pages() == 20 and m.slots.num_free == 5
+
+
+def test_block_table_changes_are_noted_and_taken_once():
+    """The device copy of a block table is kept current by change lists: every entry that changed on the host since the
+    last take comes out once, with its current value, oldest change first; a limit leaves the rest for the next take."""
+    import numpy as np
+    m = manager([FULL, WIN], pages=20, page=4, seqs=3)       # window 10
+    P = m.max_pages_per_seq
+    mirror = [np.zeros_like(g.tables).reshape(-1) for g in m.kv_groups]
+
+    def sync(limit=None):
+        for gi in range(2):
+            idx, val = m.take_table_updates(gi, limit)
+            assert len(set(idx.tolist())) == len(idx)
+            mirror[gi][idx] = val
+    a, b = m.admit("a"), m.admit("b")
+    m.ensure(a, 9)
+    m.ensure(b, 3)
+    assert m.pending_table_updates(0) == 4 and m.pending_table_updates(1) == 4
+    idx, val = m.take_table_updates(0, 3)                     # a limit: the oldest three
+    assert idx.tolist() == [a.slot * P, a.slot * P + 1, a.slot * P + 2] and m.pending_table_updates(0) == 1
+    mirror[0][idx] = val
+    sync()
+    assert all((mirror[gi] == m.kv_groups[gi].tables.reshape(-1)).all() for gi in range(2))
+    for n in range(10, 40):                                   # growth: at most one new and (window) one released entry a step
+        m.ensure(a, n)
+        m.commit(a, n)
+        assert m.pending_table_updates(0) <= 1 and m.pending_table_updates(1) <= 2
+        sync()
+        assert all((mirror[gi] == m.kv_groups[gi].tables.reshape(-1)).all() for gi in range(2))
+    m.free(a)                                                 # its live entries become null: noted too
+    assert m.pending_table_updates(0) == 10
+    m.ensure(b, 5)
+    sync()
+    assert all((mirror[gi] == m.kv_groups[gi].tables.reshape(-1)).all() for gi in range(2))
+    assert not m.kv_groups[0].tables[a.slot].any()
+    m.check_invariants()
+
+
+def test_admission_counts_what_a_request_holds_at_its_peak():
+    """A windowed group holds at most the window plus one step's span in pages, so with a bounded span a long request
+    is charged that, not its whole length; an unbounded step (whole prompts) is charged in full.  State is counted in bytes."""
+    import torch
+    m = CacheManager([FULL, WIN, StateNeed((3, 8), "float32"), StateNeed((5,), "compute")], 4, 30, 2, 4096,
+                     dtype=torch.bfloat16, allocate=False)
+    full, win = m.kv_groups
+    assert m.peak_pages(full, 100, 8) == 25 and m.peak_pages(win, 100, None) == 25
+    assert m.peak_pages(win, 100, 8) == 6                     # ceil((10 + 8) / 4) + 1
+    assert m.peak_pages(win, 9, 8) == 3                       # never more than the request itself
+    assert m.can_admit(100, 8)
+    a = m.admit("a", 100, 8)
+    m.ensure(a, 8)
+    for g in m.kv_groups:                                     # leave 26 free pages in the full group, 5 in the windowed one
+        pass
+    while win.pool.num_free > 5:
+        win.pool.take()
+    assert not m.can_admit(100, 8) and m.can_admit(9, 8)      # 6 > 5 free pages in the windowed group; 3 fit
+    assert m.state_bytes_per_seq() == 3 * 8 * 4 + 5 * 2
+    assert m.bytes_per_token() == 2 * 2 * 2 * 16 * 2

@@ -143,3 +143,36 @@ def test_missing_files(tmp_path):
     _, spec = load_config(str(tmp_path))
     with pytest.raises(FileNotFoundError):
         load_into(DecoderModel(spec), str(tmp_path), torch.float32, "cpu")
+
+
+def test_sharded_checkpoint_with_an_index(tmp_path):
+    """A folder with model.safetensors.index.json and several shard files loads the same tensors as the single file."""
+    single = str(tmp_path / "single")
+    write_random_model(TINY_B, single, seed=1, std=0.05)
+    files = open_model_tensors(single)
+    tensors = {name: f.get(name) for name, f in files.items()}
+    next(iter(files.values())).close()
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    with open(os.path.join(single, "config.json")) as f:
+        (sharded / "config.json").write_text(f.read())
+    names = sorted(tensors)
+    shards = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+              "model-00003-of-00003.safetensors": names[2::3]}
+    weight_map = {}
+    for fn, part in shards.items():
+        write_safetensors(str(sharded / fn), {n: tensors[n] for n in part})
+        weight_map.update({n: fn for n in part})
+    (sharded / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    a, b = (DecoderModel(load_config(d)[1]) for d in (single, str(sharded)))
+    load_into(a, single, torch.float32, "cpu")
+    info = load_into(b, str(sharded), torch.float32, "cpu")
+    assert info["tensors"] == len(names)
+    assert torch.equal(a.embedding, b.embedding) and torch.equal(a.lm_head, b.lm_head)
+    for x, y in zip(a.blocks, b.blocks):
+        assert torch.equal(x.mixer.qkv, y.mixer.qkv) and torch.equal(x.feed_forward.down, y.feed_forward.down)
+    # a tensor the index names in a shard that lacks it is reported like any missing tensor
+    weight_map[names[0]] = "model-00002-of-00003.safetensors"
+    (sharded / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(WeightError, match="missing"):
+        load_into(DecoderModel(load_config(str(sharded))[1]), str(sharded), torch.float32, "cpu")
