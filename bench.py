@@ -229,6 +229,17 @@ def logit_check(llm, torch, LLM, cfg, vocab, prompt_len=512, steps=8):
         llm.cache.commit(seq, seq.num_tokens + 1)
     llm.cache.free(seq)
     got = torch.stack(got)
+    # the same steps on the plainest bfloat16 path (eager, library products, nothing deferred): what 16-bit rounding
+    # alone costs at this depth, to read the timed path's error against
+    saved = (llm.ops._linear_choice, llm.ops.defer_sums, llm.ops.stream_gemm, llm.ops.skinny_gemm)
+    llm.ops._linear_choice, llm.ops.defer_sums, llm.ops.stream_gemm, llm.ops.skinny_gemm = None, False, False, False
+    try:
+        seq = llm.cache.admit(("check", 1), prompt_len + steps + 1)
+        llm.runner.step([StepEntry(seq, ids[:prompt_len], [])])
+        base = torch.cat([llm.runner.step([StepEntry(seq, [ids[prompt_len + k]], [0])]).float() for k in range(steps)])
+        llm.cache.free(seq)
+    finally:
+        llm.ops._linear_choice, llm.ops.defer_sums, llm.ops.stream_gemm, llm.ops.skinny_gemm = saved
     ref_llm = LLM(None, random_config=cfg, random_seed=0, dtype="float32", device="cuda:0", kv_block_size=16,
                   kv_cache_tokens=2048, kv_watermark=0.0, max_num_seqs=1, max_model_len=2048, cuda_graphs=False,
                   random_draw_dtype="bfloat16")
@@ -236,7 +247,9 @@ def logit_check(llm, torch, LLM, cfg, vocab, prompt_len=512, steps=8):
     del ref_llm
     err = ((got - ref).abs().max() / ref.abs().max()).item()
     agree = int((got.argmax(-1) == ref.argmax(-1)).sum())
-    return {"logit_rel_err_vs_fp32": round(err, 5), "argmax_agree": f"{agree}/{steps}", "rows": steps, "context": prompt_len}
+    base_err = ((base - ref).abs().max() / ref.abs().max()).item()
+    return {"logit_rel_err_vs_fp32": round(err, 5), "library_bf16_path_rel_err_vs_fp32": round(base_err, 5),
+            "argmax_agree": f"{agree}/{steps}", "rows": steps, "context": prompt_len}
 
 
 def reference_arm(args):

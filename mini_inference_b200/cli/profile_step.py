@@ -72,7 +72,7 @@ def main(argv=None) -> int:
             llm.ops._linear_choice = {tuple(int(v) for v in k.split(",")): c for k, c in json.load(f).items()}
     else:
         llm.ops.tune_linear(llm.model.matrix_weights(), {tuple(llm.model.lm_head.shape): torch.float32},
-                            deferrable=llm.model.deferrable_shapes())
+                            deferrable=llm.model.deferrable_shapes(), gated=llm.model.gated_shapes())
         if a.choices:
             with open(a.choices, "w") as f:
                 json.dump({",".join(str(v) for v in k): c for k, c in llm.ops._linear_choice.items()}, f)

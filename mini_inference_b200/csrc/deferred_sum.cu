@@ -108,6 +108,30 @@ __global__ void deferred_reduce_kernel(const float* __restrict__ ws, __nv_bfloat
     }
 }
 
+// out[t, j] = silu(g) * u with g = bf16(sum of shares at column j), u = bf16(sum of shares at column inter + j): the
+// gate/up product left as partial sums, the activation applied by its only reader (the two roundings are those of the
+// product stored in bfloat16 and read back by the separate activation kernel).  Four columns per thread.
+__global__ void deferred_swiglu_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int inter, int K, int G,
+                                       int max_contrib, int tok) {
+    pdl_trigger();
+    pdl_wait();
+    const int N = 2 * inter;
+    const int NKC = K / KC, NRT = (N + TR - 1) / TR;
+    const long long U = (long long)NRT * NKC;
+    const int t = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter / 4; i += gridDim.x * blockDim.x) {
+        const int n = i * 4;
+        const float4 g = sum4(ws, max_contrib, tok, shares_of(n / TR, NKC, U, G), t, n);
+        const float4 u = sum4(ws, max_contrib, tok, shares_of((inter + n) / TR, NKC, U, G), t, inter + n);
+        const float gv[4] = {bf16_round(g.x), bf16_round(g.y), bf16_round(g.z), bf16_round(g.w)};
+        const float uv[4] = {bf16_round(u.x), bf16_round(u.y), bf16_round(u.z), bf16_round(u.w)};
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = gv[e] / (1.f + expf(-gv[e])) * uv[e];
+        *reinterpret_cast<uint2*>(out + (size_t)t * inter + n) = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
+    }
+}
+
 }  // namespace
 
 // x [M, N] bfloat16 (contiguous) += the product held as partial sums in ws; y = rmsnorm(x) * w.  (N, K, grid, max_contrib,
@@ -138,5 +162,16 @@ MI_EXPORT int mi_deferred_reduce(const float* ws, void* out, int M, int N, int K
     if (N % 4 || K % KC || ((uintptr_t)out % 8) || ((uintptr_t)ws % 16)) return -2;
     const int blocks = (N / 4 + 255) / 256;
     return (int)launch_pdl(deferred_reduce_kernel, dim3(blocks, M), dim3(256), 0, stream, ws, (__nv_bfloat16*)out, N, K, grid,
+                           max_contrib, tokens_padded);
+}
+
+// out [M, inter] bfloat16 = silu(gate) * up where [gate | up] = the product [M, 2 inter] held as partial sums in ws.
+// inter must be a multiple of 4.
+MI_EXPORT int mi_deferred_swiglu(const float* ws, void* out, int M, int inter, int K, int grid, int max_contrib,
+                                 int tokens_padded, cudaStream_t stream) {
+    if (M == 0) return 0;
+    if (inter % 4 || K % KC || ((uintptr_t)out % 8) || ((uintptr_t)ws % 16)) return -2;
+    const int blocks = (inter / 4 + 255) / 256;
+    return (int)launch_pdl(deferred_swiglu_kernel, dim3(blocks, M), dim3(256), 0, stream, ws, (__nv_bfloat16*)out, inter, K, grid,
                            max_contrib, tokens_padded);
 }

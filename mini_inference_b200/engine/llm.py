@@ -91,7 +91,8 @@ class LLM:
         if self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_linear"):
             self.linear_tuning = self.ops.tune_linear(self.model.matrix_weights(),
                                                       {tuple(self.model.lm_head.shape): torch.float32},
-                                                      deferrable=self.model.deferrable_shapes())
+                                                      deferrable=self.model.deferrable_shapes(),
+                                                      gated=self.model.gated_shapes())
         from .graphs import DecodeGraphs
         self.graphs = DecodeGraphs(self.runner, self.args.max_num_seqs)
         self.graphs.capture()

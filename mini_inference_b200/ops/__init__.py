@@ -184,7 +184,17 @@ class CudaOps:
                 return act
             if rc != -2:
                 _check(rc, "gemm_tc_swiglu")
-        return self.swiglu(self.linear(x, w))
+        gu = self.linear(x, w, defer=True)
+        if isinstance(gu, DeferredSum):          # the few-row product left its partial sums: the activation kernel adds them
+            act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+            rc = self.lib.mi_deferred_swiglu(_p(gu.ws), _p(act), M, inter, gu.K, gu.grid, gu.max_contrib, gu.tok, self._stream())
+            if rc == 0:
+                self.launches += 1
+                return act
+            if rc != -2:
+                _check(rc, "deferred_swiglu")
+            gu = self.materialize(gu)
+        return self.swiglu(gu)
 
     def materialize(self, value):
         """The bfloat16 tensor behind a DeferredSum (anything else is returned as it is)."""
@@ -262,7 +272,7 @@ class CudaOps:
                 return b
         return 0
 
-    def tune_linear(self, weights, out_dtypes=None, iters=16, min_bytes=256 << 20, deferrable=()):
+    def tune_linear(self, weights, out_dtypes=None, iters=16, min_bytes=256 << 20, deferrable=(), gated=()):
         """Per weight shape and row-count bucket, time this package's few-row kernels against the
         library GEMM on the model's own weights and remember the fastest.  The reference does the
         same kind of start-up timing to choose a weight layout per shape
@@ -292,10 +302,15 @@ class CudaOps:
                         self.stream_gemm, self.skinny_gemm = name == "stream", name == "skinny"
                         self.skinny_max_rows, self.skinny_max_cols, self.stream_max_cols = 64, 1 << 30, 1 << 30
                         run = lambda i: self.linear(x, ws[i % len(ws)], out_dtype=od)
-                        if name == "stream" and (N, K) in deferrable and self.defer_sums and od in (None, torch.bfloat16):
+                        if (N, K) in gated:
+                            # a gate/up product is read by the activation only: the pair is timed, as it runs in a step
+                            self._linear_choice = {(M, N, K): name}
+                            run = lambda i: self.gated_linear(x, ws[i % len(ws)])
+                        elif name == "stream" and (N, K) in deferrable and self.defer_sums and od in (None, torch.bfloat16):
                             # these products are read by a norm kernel that adds the partial sums itself
                             run = lambda i: self._gemm_stream(x, ws[i % len(ws)], torch.bfloat16, defer=True)
                         times[name] = min(self._time_in_graph(run, iters) for _ in range(2))
+                        self._linear_choice = None
                     best = min(times, key=times.get)
                     if times[best] > 0.95 * times["library"]:      # an own kernel has to win clearly
                         best = "library"

@@ -43,6 +43,8 @@ a block reads the attributes, it never probes with hasattr:
                                forward() without its last product: forward == linear(rows, out_weight)
   open_weight              the tensor forward_open returns as out_weight (after load)
   first_weight             the tensor that forward() streams first (after load)
+  gated_weight             FeedForward: a [2 I, hidden] tensor that forward() hands to ctx.ops.gated_linear (its product is
+                               read by the activation only, so the start-up timing of kernels times the pair)
   accepts_deferred = True  Norm: forward hands `delta` to ctx.ops.add_rmsnorm untouched, so the block may give it the
                                result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
   takes_next_weight = True Norm: forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the block
@@ -101,6 +103,7 @@ class Part:
     offers_open = False
     open_weight = None
     first_weight = None
+    gated_weight = None
     accepts_deferred = False
     takes_next_weight = False
     step_arrays_key: Optional[str] = None

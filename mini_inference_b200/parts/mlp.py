@@ -35,6 +35,10 @@ class SwiGLU(Part):
     def first_weight(self):
         return self.gate_up
 
+    @property
+    def gated_weight(self):
+        return self.gate_up
+
     def forward(self, h, ctx):
         rows, w = self.forward_open(h, ctx)
         return ctx.ops.linear(rows, w)

@@ -104,6 +104,16 @@ class DecoderModel:
                     shapes.add((w.shape[0], w.shape[1]))
         return frozenset(shapes)
 
+    def gated_shapes(self):
+        """(N, K) of the matrices that go through ctx.ops.gated_linear."""
+        shapes = set()
+        for block in self.blocks:
+            for part in block.parts.values():
+                w = part.gated_weight
+                if isinstance(w, torch.Tensor) and w.dim() == 2:
+                    shapes.add((w.shape[0], w.shape[1]))
+        return frozenset(shapes)
+
     def step_flops(self, rows: int, pairs: int, logit_rows: int) -> int:
         """Floating-point operations of a step that feeds `rows` tokens which see `pairs` (query, key) pairs in all and
         wants logits for `logit_rows` of them: 2 per weight element and row, plus what the mixers report."""

@@ -344,3 +344,35 @@ def test_scheduler_in_bfloat16_is_judged_by_logits(tiny_dirs):
         for k, tok in enumerate(g):
             row = ref[len(p) - 1 + k]
             assert row[tok] >= row.max() - 2 * err, (k, tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_under_page_pressure(tmp_path, dtype):
+    """The long-context workload in small: 14B layer sizes (two layers), requests with prompts of ~1,500 tokens fed in
+    portions of 512, a pool too small for all of them, so that the newest is preempted and recomputed; graphs on.  float32:
+    the tokens equal those of a run with a large pool.  bfloat16: every token is judged at its position by its logits."""
+    from mini_inference_b200 import LLM, SamplingParams
+    from tests.plain import qwen3_plain as plain
+    d, cfg = sized_model(tmp_path, "14b", vocab=1031)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=200 + n) for n in (1500, 1409, 1333, 1467)]
+    runs = {}
+    small_pool = 364 * 16           # the four prompts take 359 pages, their 48 new tokens would need 371
+    for pool in (small_pool, 16384):
+        llm = LLM(d, dtype=dtype, device=DEV, kv_block_size=16, kv_cache_tokens=pool, kv_watermark=0.0, max_num_seqs=4,
+                  max_model_len=2048, chunked_prefill=True, max_batched_tokens=512, cuda_graphs=True)
+        runs[pool] = (llm.generate(prompts, SamplingParams(max_new_tokens=48)), llm.stats()["preemptions"])
+        llm.cache.check_invariants()
+        assert llm.cache.free_pages() == llm.cache.num_pages
+        llm.ops.check_errors()
+    (small, pre_small), (large, pre_large) = runs[small_pool], runs[16384]
+    assert pre_small > 0 and pre_large == 0
+    if dtype == "float32":
+        assert small == large
+        return
+    c, w = plain.load_model_dir(d)
+    for p, g in zip(prompts[:2], small[:2]):
+        ref = plain.forward_logits(c, w, p + g)[len(p) - 1:]
+        mine = llm.score(p + g).float().cpu()[len(p) - 1:]
+        err = (mine - ref).abs().max().item()
+        assert err < 5e-2 * ref.abs().max().item()
+        assert all(ref[k][t] >= ref[k].max() - 2 * err for k, t in enumerate(g))
