@@ -5,7 +5,7 @@ bench/micro/bench_attention.py (:61-167: paged decode attention over batch x con
 
     python -m mini_inference_b200.cli.microbench gemm      [--rows 1,8,64] [--size 4b]
     python -m mini_inference_b200.cli.microbench attention [--batch 1,8,64] [--ctx 4096]
-    python -m mini_inference_b200.cli.microbench chain     [--rows 8]    (the one-kernel block tail against its parts)
+    python -m mini_inference_b200.cli.microbench prefill   [--tokens 2048] [--ctx-before 0]
 
 Each line: kernel, shape, microseconds (CUDA events, after warm-up), GB/s of the bytes the
 kernel has to read, and that as a share of the measured copy bandwidth."""
@@ -100,7 +100,8 @@ def bench_attention(args, ops, peak):
             page_size=ps, tile=64, block_table=table, max_pages=pages_per_seq, seg_q_start=ar,
             seg_pos0=torch.full((B,), args.ctx - 1, dtype=torch.int32, device="cuda"),
             seg_kv_len=torch.full((B,), args.ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B],
-            prefill_tiles=None, prefill_tiles2=None, num_prefill_tiles2=0, num_decode=B, num_prefill_tiles=0, max_kv_len=args.ctx, num_tokens=B)
+            table_rows=None, prefill_tiles=torch.zeros((0, 2), dtype=torch.int32, device="cuda"), prefill_tiles2=None,
+            max_kv_len=args.ctx, num_tokens=B)
         q = torch.randn(B, H * D, device="cuda", dtype=torch.bfloat16)
         for label, flag in (("tensor-core", True), ("generic", False)):
             ops.fast_attention = flag
@@ -113,57 +114,42 @@ def bench_attention(args, ops, peak):
         del kv
 
 
-def bench_chain(args, ops, peak):
-    """The optional one-kernel block tail (out-projection, norm, gated feed-forward) against the separate kernels, and,
-    when the library was built with -DMI_CHAIN_TIMING, the time stamps of its phases (min / median / max over blocks)."""
-    import ctypes
+def bench_prefill_attention(args, ops, peak):
+    """Prompt attention over the pages: one request of --tokens tokens whose first token is at position --ctx-before
+    (a later portion of a long prompt when that is not 0), causal; TFLOP/s of the scores and weighted sums that count."""
+    import numpy as np
     cfg = SIZES[args.size]
-    h, q_dim, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["intermediate_size"]
-    layers = max(2, -(-args.rotate_mb * 2 ** 20 // ((h * q_dim + 3 * h * inter) * 2)))
-    g = torch.Generator().manual_seed(1)
-    mk = lambda *s, scale=1.0: (torch.randn(*s, generator=g) * scale).to(torch.bfloat16).cuda()
-    ws = [(mk(h, q_dim, scale=q_dim ** -0.5), mk(2 * inter, h, scale=h ** -0.5), mk(h, inter, scale=inter ** -0.5)) for _ in range(layers)]
-    nw = torch.ones(h, dtype=torch.bfloat16, device="cuda")
-    nbytes = (h * q_dim + 3 * h * inter) * 2
-    for M in args.rows:
-        attn, x = mk(M, q_dim), mk(M, h)
-
-        def parts(i):
-            w_o, w_gu, w_d = ws[i % layers]
-            y = ops.add_rmsnorm(x, ops.linear(attn, w_o, defer=True), nw, 1e-6)
-            return ops.linear(ops.swiglu(ops.linear(y, w_gu)), w_d)
-        saved = ops.decode_chain_on
-        ops.decode_chain_on = True
-        try:
-            for label, fn in (("one kernel", lambda i: ops.decode_chain(attn, ws[i % layers][0], x, nw, 1e-6, ws[i % layers][1], ws[i % layers][2])),
-                              ("separate", parts)):
-                us = timed(fn, args.iters)
-                print(f"block tail M={M:<3d} {label:11s} {us:8.2f} us {nbytes / us / 1e3:8.1f} GB/s {100 * nbytes / us / 1e3 / peak:5.1f} % of peak",
-                      flush=True)
-            if hasattr(ops.lib, "mi_decode_chain_timing"):
-                import numpy as np
-                ops.decode_chain(attn, ws[0][0], x, nw, 1e-6, ws[0][1], ws[0][2])
-                torch.cuda.synchronize()
-                buf = (ctypes.c_ulonglong * (160 * 16))()
-                ops.lib.mi_decode_chain_timing(buf)
-                st = np.array(buf, dtype=np.uint64).reshape(160, 16)[:ops.NUM_SMS].astype(np.int64)
-                rel = (st - st[:, 0].min()) / 1e3
-                names = ["start", "predecessor done", "p0 rows ready", "p0 first stage", "p0 units done", "p0 reduced",
-                         "p1 rows ready", "p1 first stage", "p1 units done", "p1 activation done", "p2 rows ready",
-                         "p2 first stage", "p2 units done", "p2 reduced", "p0 barrier", "p1 barrier"]
-                for i, name in enumerate(names):
-                    print(f"  {name:20s} min {rel[:, i].min():7.2f}  median {np.median(rel[:, i]):7.2f}  max {rel[:, i].max():7.2f} us")
-        finally:
-            ops.decode_chain_on = saved
+    H, KV, D, ps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], args.page_size
+    T, p0 = args.tokens, args.ctx_before
+    pages_per_seq = -(-(p0 + T) // ps)
+    layers = max(2, -(-args.rotate_mb * 2 ** 20 // (pages_per_seq * ps * KV * D * 4)))
+    kv = torch.randn(layers, 2, pages_per_seq + 1, KV, ps, D, device="cuda", dtype=torch.bfloat16)
+    table = (torch.randperm(pages_per_seq, device="cuda").to(torch.int32) + 1).view(1, pages_per_seq).contiguous()
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device="cuda")
+    meta = types.SimpleNamespace(
+        page_size=ps, tile=64, block_table=table, table_rows=None, max_pages=pages_per_seq, seg_q_start=t([0, T]), seg_pos0=t([p0]),
+        seg_kv_len=t([p0 + T]), decode_segs=t([]), prefill_tiles=t([(0, r) for r in range(0, T, 64)]).view(-1, 2),
+        prefill_tiles2=t([(0, r) for r in range(0, T, 128)]).view(-1, 2), max_kv_len=p0 + T, num_tokens=T)
+    q = torch.randn(T, H * D, device="cuda", dtype=torch.bfloat16)
+    flops = 4.0 * H * D * (T * p0 + T * (T + 1) / 2)
+    for label, tc, fast in (("tcgen05", True, True), ("mma.sync", False, True)):
+        ops.tc_attention, ops.fast_attention = tc, fast
+        us = timed(lambda i: ops.paged_attention(q, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D, D ** -0.5, None), args.iters)
+        print(f"prompt attention T={T} from position {p0} heads {H}/{KV} D={D} page {ps} {label:9s} {us:9.2f} us "
+              f"{flops / us / 1e6:8.1f} TFLOP/s", flush=True)
+    ops.tc_attention = ops.fast_attention = True
+    ops.check_errors()
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention", "chain"])
+    ap.add_argument("what", choices=["gemm", "attention", "prefill"])
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--batch", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
     ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048, help="prefill: tokens of the portion")
+    ap.add_argument("--ctx-before", type=int, default=0, help="prefill: tokens of the request already in the cache")
     ap.add_argument("--only", default=None, type=lambda s: s.split(","), help="gemm: only these (qkv,o,gate_up,down,lm_head)")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--iters", type=int, default=50)
@@ -173,7 +159,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    {"gemm": bench_gemm, "attention": bench_attention, "chain": bench_chain}[args.what](args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention}[args.what](args, ops, peak)
     return 0
 
 
