@@ -104,13 +104,17 @@ def bench_attention(args, ops, peak):
             max_kv_len=args.ctx, num_tokens=B)
         q = torch.randn(B, H * D, device="cuda", dtype=torch.bfloat16)
         for label, flag in (("tensor-core", True), ("generic", False)):
-            ops.fast_attention = flag
-            us = timed(lambda i: ops.paged_attention(q, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D,
-                                                     D ** -0.5, None), args.iters)
-            gbs = B * args.ctx * KV * D * 4 / us / 1e3
-            print(f"decode attention B={B:<3d} ctx={args.ctx} heads {H}/{KV} D={D} {label:12s} {us:9.2f} us "
-                  f"{gbs:8.1f} GB/s {100 * gbs / peak:5.1f} % of peak", flush=True)
-        ops.fast_attention = True
+            for splits in (args.splits or [None]):
+                if splits and not flag:
+                    continue
+                ops.fast_attention, ops.force_splits = flag, splits
+                us = timed(lambda i: ops.paged_attention(q, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D,
+                                                         D ** -0.5, None), args.iters)
+                gbs = B * args.ctx * KV * D * 4 / us / 1e3
+                print(f"decode attention B={B:<3d} ctx={args.ctx} heads {H}/{KV} D={D} {label:12s} "
+                      f"{'splits ' + str(splits) if splits else 'splits chosen'} {us:9.2f} us {gbs:8.1f} GB/s {100 * gbs / peak:5.1f} % of peak",
+                      flush=True)
+        ops.fast_attention, ops.force_splits = True, None
         del kv
 
 
@@ -152,6 +156,8 @@ def main(argv=None):
     ap.add_argument("--ctx-before", type=int, default=0, help="prefill: tokens of the request already in the cache")
     ap.add_argument("--only", default=None, type=lambda s: s.split(","), help="gemm: only these (qkv,o,gate_up,down,lm_head)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--splits", default=None, type=lambda s: [int(v) for v in s.split(",")],
+                    help="attention: time these numbers of key splits instead of the chosen one")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--rotate-mb", type=int, default=512, help="rotate through at least this many MB of operands")
     args = ap.parse_args(argv)

@@ -184,3 +184,32 @@ def test_admission_counts_what_a_request_holds_at_its_peak():
     assert not m.can_admit(100, 8) and m.can_admit(9, 8)      # 6 > 5 free pages in the windowed group; 3 fit
     assert m.state_bytes_per_seq() == 3 * 8 * 4 + 5 * 2
     assert m.bytes_per_token() == 2 * 2 * 2 * 16 * 2
+
+
+def test_a_decode_step_sends_changes_not_tables():
+    """The metadata of a graph-replayed decode step does not grow with the longest sequence the cache admits: the block
+    tables stay on the device, a step carries the entries that changed (at most a new and a released page per row)."""
+    import torch
+    from mini_inference_b200.engine.batch import BatchBuilder
+    from tests.ref_ops import TorchRefOps
+    sizes = []
+    for max_len in (2048, 32768):
+        m = CacheManager([FULL, WIN], 16, 4096, 64, max_len, dtype=torch.float32, device="cpu")
+        b = BatchBuilder(m, "cpu")
+        b.ops = TorchRefOps()
+        seqs = [m.admit(i) for i in range(8)]
+        for i, s in enumerate(seqs):
+            m.ensure(s, 1000 + 16 * i)
+            m.commit(s, 1000 + 16 * i)
+        batch = b.static(8, max_len)
+        b.flush_table_updates(0), b.flush_table_updates(1)        # what prompts left behind travels before the first decode step
+        for step in range(40):
+            for s in seqs:
+                assert m.ensure(s, s.num_tokens + 1)
+            nbytes = b.refill(batch, seqs, [1] * 8)
+            batch.apply_table_updates(b.ops)
+            for s in seqs:
+                m.commit(s, s.num_tokens + 1)
+        m.check_invariants()                                       # the device tables equal the host's
+        sizes.append(nbytes)
+    assert sizes[0] == sizes[1] and sizes[1] < 1024, sizes
