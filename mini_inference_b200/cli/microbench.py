@@ -71,14 +71,14 @@ def bench_gemm(args, ops, peak):
             od = torch.float32 if name == "lm_head" else None
             ops.skinny_max_rows, ops.skinny_max_cols = 64, 1 << 30
             for label, stream, skinny, tc in (("stream", True, False, False), ("skinny", False, True, False),
-                                              ("tcgen05", False, False, True), ("library", False, False, False)):
+                                              ("tcgen05 x2", False, False, True), ("library", False, False, False)):
                 ops.stream_gemm, ops.skinny_gemm, ops.tc_gemm = stream, skinny, tc
-                if (stream and M > 32) or (skinny and M > 64) or (tc and M < 128):
+                if (stream and M > 32) or (skinny and M > 64) or (tc and (M < 128 or od is not None)):
                     continue
                 us = timed(lambda i: ops.linear(x, ws[i % copies], out_dtype=od), args.iters)
                 gbs = N * K * 2 / us / 1e3
                 tf = 2.0 * M * N * K / us / 1e6
-                print(f"gemm {name:8s} M={M:<4d} N={N:<6d} K={K:<5d} {label:8s} {us:9.2f} us {gbs:8.1f} GB/s "
+                print(f"gemm {name:8s} M={M:<4d} N={N:<6d} K={K:<5d} {label:10s} {us:9.2f} us {gbs:8.1f} GB/s "
                       f"{100 * gbs / peak:5.1f} % of peak bandwidth {tf:8.1f} TFLOP/s", flush=True)
             ops.stream_gemm = ops.skinny_gemm = True
             ops.tc_gemm = False

@@ -86,7 +86,9 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.NUM_SMS = torch.cuda.get_device_properties(self._device_index).multi_processor_count
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
-        self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"      # many-row products on the tcgen05 kernel
+        # many-row bfloat16 products on this package's two-block tcgen05 kernel (csrc/gemm_tc2.cu) instead of the library GEMM.
+        # Off by default: 1.10 PFLOP/s at the gate/up shape against the library's 1.47 (see the kernel's notes)
+        self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"
         self.tc_min_rows = 128
         self.tc_attention = os.environ.get("MI_TC_ATTENTION", "1") == "1"    # prompt attention on the tcgen05 kernel
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
@@ -171,19 +173,20 @@ class CudaOps:
         return y
 
     def gated_linear(self, x, w):
-        """silu(g) * u with [g | u] = x @ w.T (w = [gate rows | up rows]).  Many rows: one tcgen05 kernel whose epilogue
-        applies the activation (csrc/gemm_tc.cu), so the [M, 2 I] product is never written; otherwise product, then swiglu."""
+        """silu(g) * u with [g | u] = x @ w.T (w = [gate rows | up rows]).  Many rows with the own tcgen05 GEMM switched on:
+        one kernel whose epilogue applies the activation (csrc/gemm_tc2.cu), so the [M, 2 I] product is never written;
+        otherwise product, then swiglu (or, for a few rows, the activation kernel that adds the product's partial sums)."""
         M, K = x.shape
         inter = w.shape[0] // 2
         if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
-            rc = self.lib.mi_gemm_tc_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
+            rc = self.lib.mi_gemm_tc2_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
             if rc == 0:
                 self.launches += 1
                 return act
             if rc != -2:
-                _check(rc, "gemm_tc_swiglu")
+                _check(rc, "gemm_tc2_swiglu")
         gu = self.linear(x, w, defer=True)
         if isinstance(gu, DeferredSum):          # the few-row product left its partial sums: the activation kernel adds them
             act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
@@ -377,15 +380,17 @@ class CudaOps:
         return out
 
     def _gemm_tc(self, x, w, od):
-        """tcgen05 + TMA product for many rows (csrc/gemm_tc.cu); None if the shape is not taken."""
+        """Two-block tcgen05 + TMA product for many rows (csrc/gemm_tc2.cu), bfloat16 result; None if the shape or the
+        result type is not taken."""
         M, K = x.shape
         N = w.shape[0]
+        if od != torch.bfloat16 or N % 8:
+            return None
         out = torch.empty((M, N), dtype=od, device=x.device)
-        rc = self.lib.mi_gemm_tc(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _code(od), _p(self._stream_error),
-                                 self._stream())
+        rc = self.lib.mi_gemm_tc2(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _p(self._stream_error), self._stream())
         if rc == -2:
             return None
-        _check(rc, "gemm_tc")
+        _check(rc, "gemm_tc2")
         self.launches += 1
         return out
 
@@ -394,7 +399,7 @@ class CudaOps:
         code = int(self._stream_error.item())
         if code != 0:
             self._stream_error.zero_()
-            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 11-13 gemm_tc, 21+ attention)")
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 21+ attention, 51-54 gemm_tc2)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):

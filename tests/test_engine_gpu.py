@@ -376,3 +376,26 @@ def test_long_prompts_under_page_pressure(tmp_path, dtype):
         err = (mine - ref).abs().max().item()
         assert err < 5e-2 * ref.abs().max().item()
         assert all(ref[k][t] >= ref[k].max() - 2 * err for k, t in enumerate(g))
+
+
+def test_own_tensor_core_gemm_in_the_engine(tmp_path):
+    """Prompt steps with every many-row product on this package's two-block tcgen05 GEMM (off by default: the library's is
+    faster), the gate/up product with the activation in its epilogue: same logits as the plain implementation."""
+    d, cfg = sized_model(tmp_path, "4b")
+    ids = random_tokens(cfg["vocab_size"], 700, seed=2)
+    want = plain_logits(d, ids)
+    runner = make_engine(d, 16, 64, dtype="bfloat16", device=DEV)
+    saved = runner.ops.tc_gemm
+    runner.ops.tc_gemm = True
+    calls = []
+    inner = runner.ops._gemm_tc
+    runner.ops._gemm_tc = lambda *a: calls.append(a[0].shape[0]) or inner(*a)
+    try:
+        for name, cuts in (("whole", [700]), ("portions", [300, 257, 143])):
+            got = run_cuts(runner, name, ids, cuts)
+            assert rel_err(got, want) < 5e-2, (name, rel_err(got, want))
+    finally:
+        runner.ops.tc_gemm = saved
+        del runner.ops._gemm_tc
+    runner.ops.check_errors()
+    assert calls and min(calls) >= 128          # qkv, o and down of every layer and step went through it
