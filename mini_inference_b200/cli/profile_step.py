@@ -65,6 +65,8 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         print(f"prefill {a.tokens} tokens: {start.elapsed_time(stop) / a.steps:.3f} ms")
+        own = sorted(k for k, v in (llm.many_row_tuning or {}).items() if v["best"] == "tc2")
+        print("many-row products on the own tcgen05 GEMM:", ", ".join(own) if own else "none")
         llm.ops.check_errors()
         return 0
     if a.choices and os.path.isfile(a.choices):

@@ -40,8 +40,10 @@ using namespace mi::sm100;
 
 namespace {
 
-constexpr int BM = 128, BK = 64;                 // rows per block (256 per tile), k per stage
-constexpr int A_BYTES = BM * BK * 2;
+constexpr int BM = 128, BK = 64;                 // rows per block (256 per tile), k per TMA box (128 bytes: one swizzle row)
+constexpr int KSUB = 2;                          // boxes along k per ring stage: a stage holds 128 of K
+constexpr int A_SUB = BM * BK * 2;               // bytes of one box of X
+constexpr int A_BYTES = KSUB * A_SUB;
 constexpr int T2_THREADS = 192;
 constexpr int ACC_COLS = 256;
 constexpr int OUT_BYTES = 4 * 2 * 4096;          // per epilogue warp two [32 x 64] bfloat16 boxes
@@ -100,7 +102,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int BN = sh.BN, NS = sh.NS, HALF = BN / 2;
-    const int B_BYTES = HALF * BK * 2, STAGE = A_BYTES + B_BYTES;
+    const int B_SUB = HALF * BK * 2, B_BYTES = KSUB * B_SUB, STAGE = A_BYTES + B_BYTES;
     unsigned char* stage_out = base + (size_t)NS * STAGE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + OUT_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 4);
@@ -110,7 +112,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cta_rank_in_cluster();         // 0: the block that issues the MMAs
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const int nk = sh.K / BK, tiles = sh.m_tiles * sh.n_tiles;
+    const int nk = (sh.K + KSUB * BK - 1) / (KSUB * BK), tiles = sh.m_tiles * sh.n_tiles;   // a box beyond K reads zeros
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -134,18 +136,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         // order m fastest: the pairs that run together share a few tiles of W, which then comes from memory once
         if (lane == 0) {
             const uint32_t full_even0 = map_to_rank(full0, 0);
-            int it = 0;
-            for (int tile = pair; tile < tiles && !abort_flag; tile += pairs) {
+            int s = 0, round = 0;                           // ring stage and how often the ring has been filled
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs) {
                 const int m0 = (tile % sh.m_tiles) * 2 * BM + (int)rank * BM, nt = tile / sh.m_tiles;
                 const int b_row = GATED ? (int)rank * (sh.N / 2) + nt * HALF : nt * BN + (int)rank * HALF;
-                for (int kc = 0; kc < nk; ++kc, ++it) {
-                    const int s = it % NS;
-                    if (it >= NS && !mbar_spin(empty0 + 8 * s, ((it / NS) - 1) & 1)) { atomicExch(error_word, 51); abort_flag = 1; }
-                    if (abort_flag) break;
-                    const uint32_t a_dst = stage0 + s * STAGE, b_dst = a_dst + A_BYTES;
+                for (int kc = 0; kc < nk; ++kc) {
+                    if (round > 0 && !mbar_spin(empty0 + 8 * s, (round - 1) & 1)) { atomicExch(error_word, 51); abort_flag = 1; ok = false; break; }
+                    const uint32_t a_dst = stage0 + s * STAGE, b_dst = a_dst + A_BYTES, bar = full_even0 + 8 * s;
                     if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);       // the bytes of both blocks
-                    tma_load_2d_pair(a_dst, &amap, kc * BK, m0, full_even0 + 8 * s);
-                    tma_load_2d_pair(b_dst, &bmap, kc * BK, b_row, full_even0 + 8 * s);
+#pragma unroll
+                    for (int u = 0; u < KSUB; ++u) {
+                        tma_load_2d_pair(a_dst + u * A_SUB, &amap, (kc * KSUB + u) * BK, m0, bar);
+                        tma_load_2d_pair(b_dst + u * B_SUB, &bmap, (kc * KSUB + u) * BK, b_row, bar);
+                    }
+                    if (++s == NS) { s = 0; ++round; }
                 }
             }
         }
@@ -153,25 +158,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         // ---------------- MMA issuer (even block): accumulator t & 1
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(2 * BM, BN, false);
-            int it = 0, t = 0;
-            for (int tile = pair; tile < tiles && !abort_flag; tile += pairs, ++t) {
+            // descriptors of a stage's first k-step: only the start-address field (units of 16 bytes) moves from there
+            const uint64_t desc_a0 = umma_desc_sw128(stage0, 16, 1024), desc_b0 = umma_desc_sw128(stage0 + A_BYTES, 16, 1024);
+            const uint32_t a_sub16 = A_SUB >> 4, b_sub16 = (uint32_t)B_SUB >> 4;
+            int s = 0, round = 0, t = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs, ++t) {
                 const int b = t & 1;
                 if (t >= 2 && !mbar_wait(acc_empty0 + 8 * b, ((t >> 1) - 1) & 1)) { atomicExch(error_word, 54); abort_flag = 1; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem + b * ACC_COLS;
-                for (int kc = 0; kc < nk; ++kc, ++it) {
-                    const int s = it % NS;
-                    if (!mbar_spin(full0 + 8 * s, (it / NS) & 1)) { atomicExch(error_word, 52); abort_flag = 1; }
-                    if (abort_flag) break;
+                for (int kc = 0; kc < nk; ++kc) {
+                    if (!mbar_spin(full0 + 8 * s, round & 1)) { atomicExch(error_word, 52); abort_flag = 1; ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = stage0 + s * STAGE, b_addr = a_addr + A_BYTES;
+                    const uint64_t off = (uint64_t)((uint32_t)(s * STAGE) >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_ss_pair(acc, umma_desc_sw128(a_addr + 32 * k, 16, 1024), umma_desc_sw128(b_addr + 32 * k, 16, 1024),
+                    for (int k = 0; k < KSUB * BK / 16; ++k)
+                        umma_ss_pair(acc, desc_a0 + off + (k >> 2) * a_sub16 + 2 * (k & 3), desc_b0 + off + (k >> 2) * b_sub16 + 2 * (k & 3),
                                      idesc, (kc | k) != 0);
                     umma_commit_pair(empty0 + 8 * s, 3);       // the stage is free in both blocks once these MMAs have read it
+                    if (++s == NS) { s = 0; ++round; }
                 }
-                if (abort_flag) break;
+                if (!ok) break;
                 umma_commit_pair(acc_full0 + 8 * b, 3);        // the accumulator is complete in both blocks
             }
         }
@@ -284,7 +292,7 @@ int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M,
     sh.BN = best_bn;
     const int per_tile = GATED ? sh.BN / 2 : sh.BN;
     sh.n_tiles = (n_cols + per_tile - 1) / per_tile;
-    const int stage = A_BYTES + (sh.BN / 2) * BK * 2;
+    const int stage = A_BYTES + KSUB * (sh.BN / 2) * BK * 2;
     sh.NS = (int)((smem_max - 2048 - OUT_BYTES) / stage);
     if (sh.NS > 8) sh.NS = 8;
     if (sh.NS < 2) return -2;

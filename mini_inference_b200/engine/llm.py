@@ -70,6 +70,11 @@ class LLM:
         self.eos_ids = set(self.model.spec.eos_token_ids)
         self.graphs = None
         self.linear_tuning = None
+        # which kernel runs the many-row products of prompt steps is timed on this model's weights (the few-row products
+        # of decode steps are timed when the decode graphs are made)
+        self.many_row_tuning = None
+        if self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_many_rows"):
+            self.many_row_tuning = self.ops.tune_many_rows(self.model.matrix_weights(), gated=self.model.gated_shapes())
         if args.cuda_graphs:
             self.enable_cuda_graphs()
         self.last_error = None

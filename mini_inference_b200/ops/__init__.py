@@ -86,9 +86,11 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.NUM_SMS = torch.cuda.get_device_properties(self._device_index).multi_processor_count
         self.force_splits = None             # tests set this to exercise the split merge on short contexts
-        # many-row bfloat16 products on this package's two-block tcgen05 kernel (csrc/gemm_tc2.cu) instead of the library GEMM.
-        # Off by default: 1.10 PFLOP/s at the gate/up shape against the library's 1.47 (see the kernel's notes)
-        self.tc_gemm = os.environ.get("MI_TC_GEMM", "0") == "1"
+        # many-row bfloat16 products on this package's two-block tcgen05 kernel (csrc/gemm_tc2.cu) instead of the library GEMM:
+        # MI_TC_GEMM=1 all of them, 0 none; otherwise ("auto") those that tune_many_rows found faster on this model's weights
+        self.tc_mode = os.environ.get("MI_TC_GEMM", "auto")
+        self.tc_gemm = self.tc_mode == "1"
+        self._many_choice = {}               # {(row bucket, N, K): "tc2"} from tune_many_rows; anything else: library
         self.tc_min_rows = 128
         self.tc_attention = os.environ.get("MI_TC_ATTENTION", "1") == "1"    # prompt attention on the tcgen05 kernel
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
@@ -178,7 +180,7 @@ class CudaOps:
         otherwise product, then swiglu (or, for a few rows, the activation kernel that adds the product's partial sums)."""
         M, K = x.shape
         inter = w.shape[0] // 2
-        if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+        if (self._use_tc(M, w.shape[0], K) and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
             rc = self.lib.mi_gemm_tc2_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
@@ -230,7 +232,7 @@ class CudaOps:
             self.launches += 1
             return out
         M, K = x.shape
-        if (self.tc_gemm and M >= self.tc_min_rows and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+        if (self._use_tc(M, w.shape[0], K) and K % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             out = self._gemm_tc(x, w, out_dtype or x.dtype)
             if out is not None:
@@ -268,6 +270,57 @@ class CudaOps:
         return torch.mm(x, w.t())
 
     ROW_BUCKETS = (1, 2, 4, 8, 16, 32)
+    MANY_BUCKETS = (256, 512, 1024, 2048, 4096)
+
+    def _many_bucket(self, M):
+        for b in self.MANY_BUCKETS:
+            if M <= b:
+                return b
+        return self.MANY_BUCKETS[-1]
+
+    def _use_tc(self, M, N, K):
+        if M < self.tc_min_rows:
+            return False
+        return self.tc_gemm or self._many_choice.get((self._many_bucket(M), N, K)) == "tc2"
+
+    def tune_many_rows(self, weights, gated=(), iters=6, min_bytes=64 << 20):
+        """Per weight shape and bucket of many rows (prompt steps), time the own two-block tcgen05 GEMM against the library
+        GEMM on the model's own weights and remember where the own kernel wins; a gate/up matrix is timed as the pair it
+        runs as (own kernel with the activation in its epilogue against library product + activation kernel).  Shapes of
+        less than min_bytes in all are left to the library (tiny models).  Returns the timings in microseconds."""
+        report = {}
+        if self.tc_mode != "auto":
+            return report
+        groups = {}
+        for w in weights:
+            if w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous() and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0:
+                groups.setdefault((w.shape[0], w.shape[1]), []).append(w)
+        saved, table = self.tc_gemm, {}
+        try:
+            self._many_choice = {}
+            for (N, K), ws in groups.items():
+                if len(ws) * N * K * 2 < min_bytes:
+                    continue
+                for M in self.MANY_BUCKETS:
+                    if M * N * 2 > 512 << 20:              # a vocabulary-wide product never has this many rows
+                        continue
+                    x = torch.randn(M, K, device=ws[0].device, dtype=torch.bfloat16)
+                    times = {}
+                    for name in ("library", "tc2"):
+                        self.tc_gemm = name == "tc2"
+                        if (N, K) in gated:
+                            run = lambda i: self.gated_linear(x, ws[i % len(ws)])
+                        else:
+                            run = lambda i: self.linear(x, ws[i % len(ws)])
+                        times[name] = min(self._time_in_graph(run, iters) for _ in range(2))
+                    if times["tc2"] < 0.97 * times["library"]:
+                        table[(M, N, K)] = "tc2"
+                    report[f"{N}x{K} M<={M}"] = {k: round(v, 1) for k, v in times.items()} | {"best": table.get((M, N, K), "library")}
+        finally:
+            self.tc_gemm = saved
+        self._many_choice = table
+        self.check_errors()
+        return report
 
     def _row_bucket(self, M):
         for b in self.ROW_BUCKETS:
