@@ -23,13 +23,18 @@
 // the next tile's products.  Every mbarrier wait is bounded; a wait that runs out raises the error word and
 // every role leaves its loop; both blocks always reach the closing cluster barrier.
 //
-// Measured (2,048 rows, Qwen3-4B shapes, graph-timed): gate/up 185 us = 1.10 PFLOP/s, qkv 69 us = 0.93 (192 tiles on
-// 74 pairs: 2.6 waves), against the library's 138 us = 1.47 and 47 us = 1.37.  With the loads taken out the same
-// instruction stream runs in 141 us (1.44 PFLOP/s), with the epilogue taken out as well no faster, and with only the X
-// loads or only the W loads still 191 us: the gap to the library is in the load -> MMA hand-over per 64 of K, not in the
-// bytes, the ring depth (3 stages: 199 us, 6: 191) or the epilogue.  Tiles narrower than 256 columns lose outright: an MMA of
-// 128 columns takes ~150 clocks where 64 are nominal.  So the engine leaves prompt-step products on the library GEMM unless
-// MI_TC_GEMM=1.
+// A ring stage holds 128 of K (two boxes per operand): one hand-over between loader and MMA thread per eight MMAs.
+// Tiles left over after the whole waves (fewer tiles than pairs, or tiles mod pairs) are cut along K between the pairs
+// when K is long enough to pay for it: every share writes its float32 accumulator to a workspace, and once a counter
+// says that all shares of a tile are there, the shares' epilogue warps each add up and store a few [32 x 32] units of
+// it, shares in order (the same bits on every run).
+//
+// Measured (Qwen3-4B shapes, graph-timed, microseconds own / library): 2,048 rows qkv 45.6 / 45.5, gate/up 138 / 138
+// (1.48 PFLOP/s), o 37 / 31, down 74 / 72; 4,096 rows gate/up 257 / 292-326, qkv 89 / 88; 256-1,024 rows the library
+// is 5-50 % faster.  With the activation in the epilogue the gate/up kernel replaces the library product and a 27 us
+// activation kernel.  What made the difference (gate/up, 2,048 rows): 256-column tiles only (an MMA of 128 columns takes
+// ~150 clocks where 64 are nominal; 185 us with them), no index arithmetic between the MMAs of a stage (164), stages of
+// 128 of K (137).  The engine times both kernels per shape and row bucket at start-up and keeps the faster.
 #include "sm100.cuh"
 #include <map>
 #include <mutex>
@@ -93,12 +98,30 @@ struct T2Shape {
     int M, N, K;                        // N: rows of W (in the gated mode 2 I)
     int BN, NS;
     int m_tiles, n_tiles;               // tiles of 256 rows x (BN or BN/2 result columns)
+    int pairs;                          // pairs of blocks launched
+    int full_waves, rem, split;         // tiles = full_waves * pairs + rem; each of the last rem tiles is cut along K between `split` pairs
 };
+
+// what pair `pair` does in its w-th turn: a whole tile (part < 0), or the k-steps [kc0, kc1) of one of the last tiles
+struct T2Work { int tile, kc0, kc1, part; };
+__device__ __forceinline__ bool t2_work(const T2Shape& sh, int pair, int w, int nk, T2Work& o) {
+    o.kc0 = 0; o.kc1 = nk; o.part = -1;
+    if (w < sh.full_waves) { o.tile = w * sh.pairs + pair; return true; }
+    if (w > sh.full_waves || pair >= sh.rem * sh.split) return false;
+    o.tile = sh.full_waves * sh.pairs + pair / sh.split;
+    if (sh.split > 1) {
+        o.part = pair % sh.split;
+        o.kc0 = o.part * nk / sh.split;
+        o.kc1 = (o.part + 1) * nk / sh.split;
+    }
+    return true;
+}
 
 template <bool GATED>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
-                const __grid_constant__ CUtensorMap omap, const T2Shape sh, int* __restrict__ error_word) {
+                const __grid_constant__ CUtensorMap omap, const T2Shape sh, __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ ws,
+                int* __restrict__ counters, int* __restrict__ error_word) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int BN = sh.BN, NS = sh.NS, HALF = BN / 2;
@@ -111,8 +134,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const uint32_t acc_full0 = smem_u32(bars + 2 * NS), acc_empty0 = smem_u32(bars + 2 * NS + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cta_rank_in_cluster();         // 0: the block that issues the MMAs
-    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const int nk = (sh.K + KSUB * BK - 1) / (KSUB * BK), tiles = sh.m_tiles * sh.n_tiles;   // a box beyond K reads zeros
+    const int pair = blockIdx.x >> 1;
+    const int nk = (sh.K + KSUB * BK - 1) / (KSUB * BK);   // a box beyond K reads zeros
+    T2Work wk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -138,10 +162,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             const uint32_t full_even0 = map_to_rank(full0, 0);
             int s = 0, round = 0;                           // ring stage and how often the ring has been filled
             bool ok = true;
-            for (int tile = pair; tile < tiles && ok; tile += pairs) {
-                const int m0 = (tile % sh.m_tiles) * 2 * BM + (int)rank * BM, nt = tile / sh.m_tiles;
+            for (int w = 0; ok && t2_work(sh, pair, w, nk, wk); ++w) {
+                const int m0 = (wk.tile % sh.m_tiles) * 2 * BM + (int)rank * BM, nt = wk.tile / sh.m_tiles;
                 const int b_row = GATED ? (int)rank * (sh.N / 2) + nt * HALF : nt * BN + (int)rank * HALF;
-                for (int kc = 0; kc < nk; ++kc) {
+                for (int kc = wk.kc0; kc < wk.kc1; ++kc) {
                     if (round > 0 && !mbar_spin(empty0 + 8 * s, (round - 1) & 1)) { atomicExch(error_word, 51); abort_flag = 1; ok = false; break; }
                     const uint32_t a_dst = stage0 + s * STAGE, b_dst = a_dst + A_BYTES, bar = full_even0 + 8 * s;
                     if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);       // the bytes of both blocks
@@ -161,21 +185,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             // descriptors of a stage's first k-step: only the start-address field (units of 16 bytes) moves from there
             const uint64_t desc_a0 = umma_desc_sw128(stage0, 16, 1024), desc_b0 = umma_desc_sw128(stage0 + A_BYTES, 16, 1024);
             const uint32_t a_sub16 = A_SUB >> 4, b_sub16 = (uint32_t)B_SUB >> 4;
-            int s = 0, round = 0, t = 0;
+            int s = 0, round = 0;
             bool ok = true;
-            for (int tile = pair; tile < tiles && ok; tile += pairs, ++t) {
+            for (int t = 0; ok && t2_work(sh, pair, t, nk, wk); ++t) {
                 const int b = t & 1;
                 if (t >= 2 && !mbar_wait(acc_empty0 + 8 * b, ((t >> 1) - 1) & 1)) { atomicExch(error_word, 54); abort_flag = 1; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem + b * ACC_COLS;
-                for (int kc = 0; kc < nk; ++kc) {
+                for (int kc = wk.kc0; kc < wk.kc1; ++kc) {
                     if (!mbar_spin(full0 + 8 * s, round & 1)) { atomicExch(error_word, 52); abort_flag = 1; ok = false; break; }
                     tc_fence_after();
                     const uint64_t off = (uint64_t)((uint32_t)(s * STAGE) >> 4);
 #pragma unroll
                     for (int k = 0; k < KSUB * BK / 16; ++k)
                         umma_ss_pair(acc, desc_a0 + off + (k >> 2) * a_sub16 + 2 * (k & 3), desc_b0 + off + (k >> 2) * b_sub16 + 2 * (k & 3),
-                                     idesc, (kc | k) != 0);
+                                     idesc, ((kc - wk.kc0) | k) != 0);
                     umma_commit_pair(empty0 + 8 * s, 3);       // the stage is free in both blocks once these MMAs have read it
                     if (++s == NS) { s = 0; ++round; }
                 }
@@ -187,67 +211,160 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         // ---------------- epilogue (both blocks): warp w reads tensor-memory lanes 32 (w % 4) .. +31, one row per thread
         const int lg = warp & 3;
         const uint32_t acc_empty_even0 = map_to_rank(acc_empty0, 0);
-        int t = 0, groups = 0;
+        int groups = 0;
         unsigned char* my_out = stage_out + (warp - 2) * 8192;
         const int per_tile = GATED ? HALF : BN;                        // result columns of a tile
         const int n_out = GATED ? sh.N / 2 : sh.N;
-        for (int tile = pair; tile < tiles && !abort_flag; tile += pairs, ++t) {
+        // 64 values per thread (row row0 + lane, columns col .. col + 63) -> a swizzled [32 x 64] bfloat16 box -> TMA store
+        auto put_box = [&](const float (&v)[64], int col, int row0) {
+            unsigned char* box = my_out + (groups & 1) * 4096;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");   // the store two boxes back has read its box
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 p;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&p);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+                    pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) = p;
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                if (col < n_out && row0 < sh.M) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];\n"
+                                 :: "l"((uint64_t)&omap), "r"(col), "r"(row0), "r"(smem_u32(box)) : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            }
+            ++groups;
+        };
+        auto activate = [](float gate, float up) {
+            const float gt = round_to<__nv_bfloat16>(gate), u = round_to<__nv_bfloat16>(up);
+            return gt / (1.f + expf(-gt)) * u;
+        };
+        for (int t = 0; !abort_flag && t2_work(sh, pair, t, nk, wk); ++t) {
             const int b = t & 1;
-            const int m0 = (tile % sh.m_tiles) * 2 * BM + (int)rank * BM, nt = tile / sh.m_tiles;
+            const int m0 = (wk.tile % sh.m_tiles) * 2 * BM + (int)rank * BM, nt = wk.tile / sh.m_tiles;
             if (!mbar_wait(acc_full0 + 8 * b, (t >> 1) & 1)) { atomicExch(error_word, 53); abort_flag = 1; break; }
             tc_fence_after();
             const uint32_t acc = tmem + ((uint32_t)(lg * 32) << 16) + b * ACC_COLS;
-            for (int c = 0; c < per_tile / 64; ++c) {
-                float v[64];
+            if (wk.part < 0) {
+                for (int c = 0; c < per_tile / 64; ++c) {
+                    float v[64];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int col_in = c * 64 + h * 32;
-                    uint32_t ra[32];
-                    tmem_ld32(acc + col_in, ra);
-                    if (GATED) {
-                        uint32_t ru[32];
-                        tmem_ld32(acc + HALF + col_in, ru);
-                        tmem_wait_ld();
+                    for (int h = 0; h < 2; ++h) {
+                        const int col_in = c * 64 + h * 32;
+                        uint32_t ra[32];
+                        tmem_ld32(acc + col_in, ra);
+                        if (GATED) {
+                            uint32_t ru[32];
+                            tmem_ld32(acc + HALF + col_in, ru);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float gt = round_to<__nv_bfloat16>(__uint_as_float(ra[i])), up = round_to<__nv_bfloat16>(__uint_as_float(ru[i]));
-                            v[h * 32 + i] = gt / (1.f + expf(-gt)) * up;
+                            for (int i = 0; i < 32; ++i) v[h * 32 + i] = activate(__uint_as_float(ra[i]), __uint_as_float(ru[i]));
+                        } else {
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[h * 32 + i] = __uint_as_float(ra[i]);
                         }
-                    } else {
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[h * 32 + i] = __uint_as_float(ra[i]);
                     }
+                    put_box(v, nt * per_tile + c * 64, m0 + lg * 32);
                 }
-                unsigned char* box = my_out + (groups & 1) * 4096;
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");   // the store two boxes back has read its box
+                tc_fence_before();
                 __syncwarp();
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint4 p;
-                    uint32_t* w = reinterpret_cast<uint32_t*>(&p);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
-                        w[e] = *reinterpret_cast<uint32_t*>(&hh);
-                    }
-                    *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) = p;
-                }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
-                    const int col = nt * per_tile + c * 64, row0 = m0 + lg * 32;
-                    if (col < n_out && row0 < sh.M) {
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];\n"
-                                     :: "l"((uint64_t)&omap), "r"(col), "r"(row0), "r"(smem_u32(box)) : "memory");
-                    }
-                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-                }
-                ++groups;
+                if (lane == 0) mbar_arrive_cluster(acc_empty_even0 + 8 * b);   // this warp has read its lanes of the accumulator
+                continue;
             }
-            tc_fence_before();
+            // ---- one of `split` shares of a tile: the share goes to the workspace as float32, [32-column group][column][row]
+            // so that a warp's stores and loads are whole lines; when all shares of this block's rows are there (a counter
+            // per tile and block rank), each share's block adds up and stores some of the tile's boxes, shares in order
+            const int tr = wk.tile - sh.full_waves * sh.pairs, groups32 = BN / 32;
+            const size_t share_floats = (size_t)BM * BN;
+            float* mine = ws + ((size_t)(tr * sh.split + wk.part) * 2 + rank) * share_floats;
+            for (int a = 0; a < groups32; ++a) {
+                uint32_t ra[32];
+                tmem_ld32(acc + a * 32, ra);
+                tmem_wait_ld();
+                float* dst = mine + (size_t)(lg * groups32 + a) * 1024 + lane;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) __stcg(dst + i * 32, __uint_as_float(ra[i]));
+            }
+            __threadfence();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty_even0 + 8 * b);   // this warp has read its lanes of the accumulator
+            int* ctr = counters + tr * 2 + rank;
+            const int need = 4 * sh.split;                 // four epilogue warps in each share's block
+            if (lane == 0) {
+                atomicAdd(ctr, 1);
+                bool seen = false;
+                for (uint32_t i = 0; i < (1u << 21) && !seen; ++i) {
+                    int have;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(have) : "l"(ctr) : "memory");
+                    seen = have >= need;
+                    if (!seen) __nanosleep(40);
+                }
+                if (!seen) { atomicExch(error_word, 55); abort_flag = 1; }
+            }
+            __syncwarp();
+            __threadfence();
+            if (!abort_flag) {
+                // units of [32 rows x 32 result columns], dealt round to the 4 * split epilogue warps of the shares' blocks;
+                // four shares' loads are in flight at a time (one warp's chain of round trips to L2 is what this costs)
+                const int gpt = per_tile / 32, units = 4 * gpt, workers = 4 * sh.split;
+                auto add_up = [&](float (&sum)[32], const float* src) {      // src: share 0's group; the shares lie share_floats * 2 apart
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sum[i] = 0.f;
+                    for (int j = 0; j < sh.split; j += 4) {
+                        float part[4][32];
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) {
+                            const bool there = j + d < sh.split;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) part[d][i] = there ? __ldcg(src + (size_t)(j + d) * 2 * share_floats + i * 32) : 0.f;
+                        }
+#pragma unroll
+                        for (int d = 0; d < 4; ++d)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) sum[i] += part[d][i];
+                    }
+                };
+                const float* tile_ws = ws + ((size_t)(tr * sh.split) * 2 + rank) * share_floats + lane;
+                for (int unit = wk.part * 4 + (warp - 2); unit < units; unit += workers) {
+                    const int lq = unit / gpt, a = unit % gpt;
+                    float g[32];
+                    add_up(g, tile_ws + (size_t)(lq * groups32 + a) * 1024);
+                    if (GATED) {
+                        float u[32];
+                        add_up(u, tile_ws + (size_t)(lq * groups32 + HALF / 32 + a) * 1024);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) g[i] = activate(g[i], u[i]);
+                    }
+                    const int row = m0 + lq * 32 + lane, col = nt * per_tile + a * 32;
+                    if (row < sh.M && col < n_out) {
+                        __nv_bfloat16* dst = out + (size_t)row * ldo + col;
+                        if (col + 32 <= n_out) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 p;
+                                uint32_t* pw = reinterpret_cast<uint32_t*>(&p);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    __nv_bfloat162 hh = __floats2bfloat162_rn(g[8 * j + 2 * e], g[8 * j + 2 * e + 1]);
+                                    pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+                                }
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = p;
+                            }
+                        } else {
+                            for (int i = 0; i < n_out - col; ++i) dst[i] = __float2bfloat16_rn(g[i]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && !abort_flag && atomicAdd(ctr, 1) == 2 * need - 1) atomicExch(ctr, 0);   // the last reader leaves the counter as it found it
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // the stores have landed
     }
@@ -260,7 +377,8 @@ std::mutex t2_mutex;
 std::map<std::tuple<const void*, int, int, int>, CUtensorMap> t2_weight_maps;
 
 template <bool GATED>
-int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K, int* error_word, cudaStream_t stream) {
+int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K, float* ws, long long ws_bytes,
+               int* counters, int num_counters, int* error_word, cudaStream_t stream) {
     const int n_cols = GATED ? N / 2 : N;
     if (ldo % 8 || ((uintptr_t)out % 16)) return -2;
     T2Shape sh;
@@ -311,8 +429,23 @@ int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M,
     }
     if (!sm100_host::make_map_bf16(&omap, out, M, n_cols, ldo, 32, 64)) return -5;
     const size_t smem = (size_t)sh.NS * stage + OUT_BYTES + (2 * sh.NS + 4) * 8 + 16 + 1024;
-    const int tiles = sh.m_tiles * sh.n_tiles;
-    const int pairs = tiles < pairs_max ? tiles : pairs_max;
+    // whole waves of tiles, one per pair; the tiles left over (or all of them, if there are fewer than pairs) are cut
+    // along K between as many pairs as there are for each, so the last wave is as long as its share of K
+    const int tiles = sh.m_tiles * sh.n_tiles, nk = (K + KSUB * BK - 1) / (KSUB * BK);
+    sh.full_waves = tiles / pairs_max;
+    sh.rem = tiles % pairs_max;
+    sh.split = 1;
+    if (sh.rem > 0 && ws && counters && 2 * sh.rem <= num_counters && ((uintptr_t)ws % 16) == 0) {
+        int split = pairs_max / sh.rem;
+        if (split > nk / 2) split = nk / 2;
+        if (split > 16) split = 16;
+        const long long share = 2ll * BM * sh.BN * 4;
+        while (split > 1 && (long long)sh.rem * split * share > ws_bytes) --split;
+        // a cut saves (1 - 1/split) of a tile's time (~0.7 us per 128 of K) and costs ~10 us for the pass through the workspace
+        if (split >= 2 && (long long)nk * (split - 1) >= 16ll * split) sh.split = split;
+    }
+    const int pairs = sh.full_waves > 0 ? pairs_max : sh.rem * sh.split;
+    sh.pairs = pairs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(T2_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -321,23 +454,25 @@ int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M,
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 2;
-    return (int)cudaLaunchKernelEx(&cfg, kern, amap, bmap, omap, sh, error_word);
+    return (int)cudaLaunchKernelEx(&cfg, kern, amap, bmap, omap, sh, (__nv_bfloat16*)out, ldo, ws, counters, error_word);
 }
 
 }  // namespace
 
 // bfloat16 result.  Returns -2 for shapes it does not take (K not a multiple of 64, unaligned rows): the caller uses another GEMM.
-MI_EXPORT int mi_gemm_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K, int* error_word,
-                          cudaStream_t stream) {
+// ws (ws_bytes, 16-byte aligned) and counters (num_counters ints, zero) may be null: scratch for cutting the last tiles along K.
+// Launches that share them must be ordered on one stream.
+MI_EXPORT int mi_gemm_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N, int K, float* ws,
+                          long long ws_bytes, int* counters, int num_counters, int* error_word, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     if (K % BK || K < BK || ldx % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return -2;
-    return launch_tc2<false>(X, ldx, W, out, ldo, M, N, K, error_word, stream);
+    return launch_tc2<false>(X, ldx, W, out, ldo, M, N, K, ws, ws_bytes, counters, num_counters, error_word, stream);
 }
 
 // act[M, I] = silu(g) * u with [g | u] = X[M, K] * W[2 I, K]^T (both rounded to bfloat16 first, as the separate kernels do).
-MI_EXPORT int mi_gemm_tc2_swiglu(const void* X, int ldx, const void* W, void* act, int M, int inter, int K, int* error_word,
-                                 cudaStream_t stream) {
+MI_EXPORT int mi_gemm_tc2_swiglu(const void* X, int ldx, const void* W, void* act, int M, int inter, int K, float* ws,
+                                 long long ws_bytes, int* counters, int num_counters, int* error_word, cudaStream_t stream) {
     if (M == 0 || inter == 0) return 0;
     if (K % BK || K < BK || ldx % 8 || inter % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16) || ((uintptr_t)act % 16)) return -2;
-    return launch_tc2<true>(X, ldx, W, act, inter, M, 2 * inter, K, error_word, stream);
+    return launch_tc2<true>(X, ldx, W, act, inter, M, 2 * inter, K, ws, ws_bytes, counters, num_counters, error_word, stream);
 }

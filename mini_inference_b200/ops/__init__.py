@@ -92,6 +92,9 @@ class CudaOps:
         self.tc_gemm = self.tc_mode == "1"
         self._many_choice = {}               # {(row bucket, N, K): "tc2"} from tune_many_rows; anything else: library
         self.tc_min_rows = 128
+        # scratch of the own GEMM for the tiles it cuts along K (the shares of a last, partly filled wave of tiles)
+        self._tc2_ws = torch.empty(20 << 20, dtype=torch.uint8, device=self.device)
+        self._tc2_counters = torch.zeros(512, dtype=torch.int32, device=self.device)
         self.tc_attention = os.environ.get("MI_TC_ATTENTION", "1") == "1"    # prompt attention on the tcgen05 kernel
         self.stream_gemm = True              # few-row products on the persistent TMA weight-streaming kernel
         self.stream_max_cols = int(os.environ.get("MI_STREAM_MAX_COLS", 1 << 30))
@@ -183,7 +186,7 @@ class CudaOps:
         if (self._use_tc(M, w.shape[0], K) and K % 64 == 0 and inter % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
             act = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
-            rc = self.lib.mi_gemm_tc2_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, _p(self._stream_error), self._stream())
+            rc = self.lib.mi_gemm_tc2_swiglu(_p(x), x.stride(0), _p(w), _p(act), M, inter, K, *self._tc2_scratch(), _p(self._stream_error), self._stream())
             if rc == 0:
                 self.launches += 1
                 return act
@@ -440,19 +443,23 @@ class CudaOps:
         if od != torch.bfloat16 or N % 8:
             return None
         out = torch.empty((M, N), dtype=od, device=x.device)
-        rc = self.lib.mi_gemm_tc2(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, _p(self._stream_error), self._stream())
+        rc = self.lib.mi_gemm_tc2(_p(x), x.stride(0), _p(w), _p(out), N, M, N, K, *self._tc2_scratch(), _p(self._stream_error), self._stream())
         if rc == -2:
             return None
         _check(rc, "gemm_tc2")
         self.launches += 1
         return out
 
+    def _tc2_scratch(self):
+        return (_p(self._tc2_ws), _c.c_longlong(self._tc2_ws.numel()), _p(self._tc2_counters), self._tc2_counters.numel())
+
     def check_errors(self):
         """Raises if a bounded wait inside a kernel ran out (synchronises the device)."""
         code = int(self._stream_error.item())
         if code != 0:
             self._stream_error.zero_()
-            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 21+ attention, 51-54 gemm_tc2)")
+            self._tc2_counters.zero_()
+            raise RuntimeError(f"a pipeline wait inside a kernel ran out (code {code}: 1-2 gemm_stream, 21+ attention, 51-55 gemm_tc2)")
 
     # ---------------------------------------------------------------- q/k norm, rotation, cache write
     def qk_norm_rope_cache(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):

@@ -179,7 +179,8 @@ def test_gemm_stream(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 512, 128), (700, 517 + 3, 192), (2048, 2560, 4096), (2048, 6144, 2560),
-                                   (513, 304, 640), (1027, 2560, 9728), (128, 128, 128), (129, 296, 640), (1, 256, 64), (300, 6144, 2560)])
+                                   (513, 304, 640), (1027, 2560, 9728), (128, 128, 128), (129, 296, 640), (1, 256, 64), (300, 6144, 2560),
+                                   (256, 2560, 4096), (4096, 2560, 1024), (1500, 1288, 448)])
 def test_gemm_tc2(ops, M, N, K):
     """The two-block (cta_group::2) tcgen05 product: 256-row tiles shared by a cluster of two blocks."""
     g = torch.Generator().manual_seed(M + N)
@@ -193,10 +194,12 @@ def test_gemm_tc2(ops, M, N, K):
     want = x.double() @ w.double().T
     close(got, want, torch.bfloat16)
     assert torch.equal(got, again)
+    assert int(ops._tc2_counters.abs().sum()) == 0               # tiles cut along K leave their arrival counters at zero
     assert ops._gemm_tc(x, w, torch.float32) is None             # bfloat16 results only: the caller takes another kernel
 
 
-@pytest.mark.parametrize("M,inter,K", [(512, 128, 64), (700, 264, 192), (2048, 9728, 2560), (600, 1000, 640), (513, 40, 128), (129, 64, 128)])
+@pytest.mark.parametrize("M,inter,K", [(512, 128, 64), (700, 264, 192), (2048, 9728, 2560), (600, 1000, 640), (513, 40, 128), (129, 64, 128),
+                                       (256, 1024, 2560), (1024, 648, 512)])
 def test_gemm_tc2_swiglu(ops, M, inter, K):
     """The same with the gate rows loaded by the even block and the up rows by the odd one, silu(gate) * up in the epilogue."""
     g = torch.Generator().manual_seed(M + inter)
