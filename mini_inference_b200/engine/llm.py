@@ -74,7 +74,7 @@ class LLM:
         # of decode steps are timed when the decode graphs are made)
         self.many_row_tuning = None
         if self.dtype == torch.bfloat16 and hasattr(self.ops, "tune_many_rows"):
-            self.many_row_tuning = self.ops.tune_many_rows(self.model.matrix_weights(), gated=self.model.gated_shapes())
+            self.many_row_tuning = self.ops.tune_many_rows(self.model.matrix_weights(), self.model.first_product_probes(self.ops))
         if args.cuda_graphs:
             self.enable_cuda_graphs()
         self.last_error = None

@@ -286,11 +286,13 @@ class CudaOps:
             return False
         return self.tc_gemm or self._many_choice.get((self._many_bucket(M), N, K)) == "tc2"
 
-    def tune_many_rows(self, weights, gated=(), iters=6, min_bytes=64 << 20):
+    def tune_many_rows(self, weights, probes=None, iters=6, min_bytes=64 << 20):
         """Per weight shape and bucket of many rows (prompt steps), time the own two-block tcgen05 GEMM against the library
-        GEMM on the model's own weights and remember where the own kernel wins; a gate/up matrix is timed as the pair it
-        runs as (own kernel with the activation in its epilogue against library product + activation kernel).  Shapes of
-        less than min_bytes in all are left to the library (tiny models).  Returns the timings in microseconds."""
+        GEMM on the model's own weights and remember where the own kernel wins.  probes: {(N, K): probe(rows) -> run(weight)}
+        for products that run together with what follows them (gate/up with its activation, q/k/v with norm, rotation and
+        cache write: own kernel with that in its epilogue against library product + separate kernel).  Shapes of less than
+        min_bytes in all are left to the library (tiny models).  Returns the timings in microseconds."""
+        probes = probes or {}
         report = {}
         if self.tc_mode != "auto":
             return report
@@ -311,8 +313,9 @@ class CudaOps:
                     times = {}
                     for name in ("library", "tc2"):
                         self.tc_gemm = name == "tc2"
-                        if (N, K) in gated:
-                            run = lambda i: self.gated_linear(x, ws[i % len(ws)])
+                        if (N, K) in probes:
+                            probe = probes[(N, K)](M)
+                            run = lambda i: probe(ws[i % len(ws)])
                         else:
                             run = lambda i: self.linear(x, ws[i % len(ws)])
                         times[name] = min(self._time_in_graph(run, iters) for _ in range(2))
@@ -507,11 +510,12 @@ class CudaOps:
                 best, best_eff = S, eff
         return best
 
-    def qk_attention(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache, owns_cache, scale, window):
-        """Per-head q/k norm, rotation, cache write, then attention over the pages."""
-        q = self.qk_norm_rope_cache(qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta,
-                                    k_cache if owns_cache else None, v_cache if owns_cache else None)
-        return self.paged_attention(q, k_cache, v_cache, meta, H, KV, D, scale, window)
+    def qkv_project(self, h, w, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):
+        """q [T, H D] (a strided view is allowed) = rotated(normed(h @ w_q.T)); rotated(normed(k)) and v go to the rows' slots
+        of the caches (None: this layer writes none).  The product, then the norm / rotation / cache-write kernel; one entry,
+        so that the start-up timing of kernels sees the pair (a version with all of it in the GEMM's epilogue was measured
+        and dropped: 76-92 us against 59 us for the pair at 2,048 rows)."""
+        return self.qk_norm_rope_cache(self.linear(h, w), H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache)
 
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
         """meta: the step's arrays for this cache group.  seg_q_start, seg_pos0, seg_kv_len per entry; decode_segs (entries

@@ -8,6 +8,8 @@ the step's pages BEFORE attention runs, so a portion attends to itself through t
 from __future__ import annotations
 
 import numpy as np
+from types import SimpleNamespace
+
 import torch
 
 from .base import KVCacheNeed, Part, WeightSpec, register_mixer
@@ -78,7 +80,18 @@ class GQAAttention(Part):
         """Everything but the output projection: (attention rows [T, H*D], o_proj weight)."""
         ops = ctx.ops
         meta = ctx.batch.group_view(cache.group, self.step_arrays_key)
-        qkv = ops.linear(h, self.qkv)
-        o = ops.qk_attention(qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
-                             position.rotary_inv_freq(), meta, cache.k, cache.v, owns_cache, self.scale, self.window)
+        q = ops.qkv_project(h, self.qkv, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps,
+                            position.rotary_inv_freq(), meta, cache.k if owns_cache else None, cache.v if owns_cache else None)
+        o = ops.paged_attention(q, cache.k, cache.v, meta, self.H, self.KV, self.D, self.scale, self.window)
         return o, self.o
+
+    def first_product_probe(self, ops, rows):
+        """The projection with norm, rotation and cache write as forward_open runs it, on a made-up cache of its own."""
+        dev, dt, page = self.qkv.device, self.qkv.dtype, 16
+        x = torch.randn(rows, self.hidden, device=dev, dtype=dt)
+        k = torch.zeros(((rows + page - 1) // page + 1, self.KV, page, self.D), device=dev, dtype=dt)
+        v = torch.zeros_like(k)
+        ar = torch.arange(rows, device=dev, dtype=torch.int32)
+        meta = SimpleNamespace(positions=ar, slots=ar + page, page_size=page)
+        inv_freq = torch.full((self.D // 2,), 0.01, device=dev, dtype=torch.float32)
+        return lambda w: ops.qkv_project(x, w, self.H, self.KV, self.D, self.q_norm, self.k_norm, self.qk_eps, inv_freq, meta, k, v)

@@ -45,6 +45,10 @@ a block reads the attributes, it never probes with hasattr:
   first_weight             the tensor that forward() streams first (after load)
   gated_weight             FeedForward: a [2 I, hidden] tensor that forward() hands to ctx.ops.gated_linear (its product is
                                read by the activation only, so the start-up timing of kernels times the pair)
+  first_product_probe(ops, rows)
+                           -> run(weight), or None.  run does what forward() does with its first weight (the product and
+                               whatever this part lets the kernel namespace fuse with it) for `rows` rows of made-up input;
+                               the start-up timing of many-row kernels then times that instead of the bare product
   accepts_deferred = True  Norm: forward hands `delta` to ctx.ops.add_rmsnorm untouched, so the block may give it the
                                result of ctx.ops.linear(..., defer=True) (possibly partial sums the kernel adds up)
   takes_next_weight = True Norm: forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the block
@@ -107,6 +111,9 @@ class Part:
     accepts_deferred = False
     takes_next_weight = False
     step_arrays_key: Optional[str] = None
+
+    def first_product_probe(self, ops, rows):
+        return None
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

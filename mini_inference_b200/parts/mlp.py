@@ -39,6 +39,10 @@ class SwiGLU(Part):
     def gated_weight(self):
         return self.gate_up
 
+    def first_product_probe(self, ops, rows):
+        x = torch.randn(rows, self.hidden, device=self.gate_up.device, dtype=self.gate_up.dtype)
+        return lambda w: ops.gated_linear(x, w)
+
     def forward(self, h, ctx):
         rows, w = self.forward_open(h, ctx)
         return ctx.ops.linear(rows, w)

@@ -114,6 +114,17 @@ class DecoderModel:
                     shapes.add((w.shape[0], w.shape[1]))
         return frozenset(shapes)
 
+    def first_product_probes(self, ops):
+        """{(N, K) of a part's first weight: probe(rows) -> run(weight)} for the parts that offer one (see Part)."""
+        probes = {}
+        for block in self.blocks:
+            for part in block.parts.values():
+                w = part.first_weight
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and (w.shape[0], w.shape[1]) not in probes:
+                    if part.first_product_probe(ops, 1) is not None:
+                        probes[(w.shape[0], w.shape[1])] = (lambda rows, part=part: part.first_product_probe(ops, rows))
+        return probes
+
     def step_flops(self, rows: int, pairs: int, logit_rows: int) -> int:
         """Floating-point operations of a step that feeds `rows` tokens which see `pairs` (query, key) pairs in all and
         wants logits for `logit_rows` of them: 2 per weight element and row, plus what the mixers report."""

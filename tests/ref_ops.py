@@ -71,10 +71,8 @@ class TorchRefOps:
             v_cache[page, :, off, :] = v
         return q.reshape(T, H * D)
 
-    def qk_attention(self, qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache, owns_cache, scale, window):
-        q = self.qk_norm_rope_cache(qkv, H, KV, D, q_weight, k_weight, eps, inv_freq, meta,
-                                    k_cache if owns_cache else None, v_cache if owns_cache else None)
-        return self.paged_attention(q, k_cache, v_cache, meta, H, KV, D, scale, window)
+    def qkv_project(self, h, w, H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache):
+        return self.qk_norm_rope_cache(self.linear(h, w), H, KV, D, q_weight, k_weight, eps, inv_freq, meta, k_cache, v_cache)
 
     # ---------------------------------------------------------------- attention over the pages
     def paged_attention(self, q, k_cache, v_cache, meta, H, KV, D, scale, window):
