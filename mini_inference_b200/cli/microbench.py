@@ -141,6 +141,21 @@ def bench_prefill_attention(args, ops, peak):
         us = timed(lambda i: ops.paged_attention(q, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D, D ** -0.5, None), args.iters)
         print(f"prompt attention T={T} from position {p0} heads {H}/{KV} D={D} page {ps} {label:9s} {us:9.2f} us "
               f"{flops / us / 1e6:8.1f} TFLOP/s", flush=True)
+        if tc and hasattr(ops.lib, "mi_attn_tc_timing"):
+            # a library built with MI_NVCC_EXTRA=-DMI_ATT_TIMING counts clocks of one softmax thread per block and key tile
+            import ctypes
+            ticks = (ctypes.c_ulonglong * 16)()
+            ops.lib.mi_attn_tc_timing(ticks, 1)
+            ops.paged_attention(q, kv[0, 0], kv[0, 1], meta, H, KV, D, D ** -0.5, None)
+            torch.cuda.synchronize()
+            ops.lib.mi_attn_tc_timing(ticks, 1)
+            n = max(1, ticks[3])
+            print(f"  softmax thread, clocks per 64-key tile over {n} tiles: wait for scores {ticks[0] / n:.0f}, "
+                  f"maximum + exponentials + P store {ticks[1] / n:.0f}, wait for the previous PV + hand-over {ticks[2] / n:.0f}", flush=True)
+            print(f"  MMA thread, clocks per tile: wait for the next keys + issue of their scores {ticks[4] / n:.0f}, wait for P {ticks[5] / n:.0f}, "
+                  f"wait for the values {ticks[6] / n:.0f}", flush=True)
+            print(f"  of the middle part: score load {ticks[8] / n:.0f}, mask + maximum {ticks[9] / n:.0f}, exponentials + sums + packing {ticks[10] / n:.0f}, "
+                  f"P store {ticks[11] / n:.0f}", flush=True)
     ops.tc_attention = ops.fast_attention = True
     ops.check_errors()
 

@@ -199,6 +199,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             tmem_ld32(lane_addr + s_col, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
             tmem_ld32(lane_addr + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
             tmem_wait_ld();
+            TICK(ta);
             // Scores stay unscaled in r[]; the scale is folded into the exponent's multiply-add.  Only tiles
             // that touch the diagonal (or the window's edge) for some row of the warp pay for masking.
             const bool inside = kt * BKV + BKV - 1 <= p_row && (window <= 0 || kt * BKV > p_row - window);
@@ -229,6 +230,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
                 l *= alpha;
             }
             const float off = m_ref == -INFINITY ? 0.f : m_ref;
+            TICK(tb);
             uint32_t pk[32];
             const float2 scale2 = make_float2(scale_log2, scale_log2), noff2 = make_float2(-off, -off);
             float2 sums[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -243,6 +245,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             const float2 s01 = __fadd2_rn(sums[0], sums[1]), s23 = __fadd2_rn(sums[2], sums[3]);
             const float sum = (s01.x + s01.y) + (s23.x + s23.y);
             l += sum;
+            TICK(tc);
             tmem_st32(lane_addr + s_col, pk);                  // P takes the place of the scores it came from
             TICK(t2);
             // Every thread follows pv_done phase by phase (a parity wait can only tell the current phase
@@ -265,7 +268,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
             mbar_arrive(p_ready);
             TICK(t3);
 #ifdef MI_ATT_TIMING
-            if (threadIdx.x == 64) { ADD(0, t0, t1); ADD(1, t1, t2); ADD(2, t2, t3); atomicAdd(&att_ticks[3], 1ull); }
+            if (threadIdx.x == 64) { ADD(0, t0, t1); ADD(1, t1, t2); ADD(2, t2, t3); atomicAdd(&att_ticks[3], 1ull);
+                                     ADD(8, t1, ta); ADD(9, ta, tb); ADD(10, tb, tc); ADD(11, tc, t2); }
 #endif
         }
         // ---------------- epilogue
