@@ -378,9 +378,39 @@ def test_long_prompts_under_page_pressure(tmp_path, dtype):
         assert all(ref[k][t] >= ref[k].max() - 2 * err for k, t in enumerate(g))
 
 
+def test_start_up_choice_of_many_row_kernels(tmp_path):
+    """The start-up timing of prompt-step products on the model's own weights: every shape and row bucket gets a verdict, the
+    parts' probes are used (gate/up with its activation, q/k/v with norm, rotation and cache write), only verdicts for the own
+    kernel are kept, and a prompt step after it still gives the plain implementation's logits."""
+    d, cfg = sized_model(tmp_path, "4b")
+    ids = random_tokens(cfg["vocab_size"], 600, seed=3)
+    want = plain_logits(d, ids)
+    runner = make_engine(d, 16, 64, dtype="bfloat16", device=DEV)
+    ops, model = runner.ops, runner.model
+    probes = model.first_product_probes(ops)
+    qkv_shape, gate_up_shape = tuple(model.blocks[0].parts["mixer"].qkv.shape), tuple(model.blocks[0].parts["feed_forward"].gate_up.shape)
+    assert set(probes) == {qkv_shape, gate_up_shape}
+    before = dict(ops._many_choice)
+    try:
+        report = ops.tune_many_rows(model.matrix_weights(), probes, iters=2, min_bytes=0)
+        shapes = {tuple(int(v) for v in k.split(" ")[0].split("x")) for k in report}
+        assert {qkv_shape, gate_up_shape} <= shapes and len(report) >= 2 * len(ops.MANY_BUCKETS)
+        assert all(v["best"] in ("library", "tc2") and v["library"] > 0 and v["tc2"] > 0 for v in report.values())
+        assert set(ops._many_choice.values()) <= {"tc2"}
+        assert sorted(ops._many_choice) == sorted((int(k.split("<=")[1]), *(int(v) for v in k.split(" ")[0].split("x")))
+                                                  for k, v in report.items() if v["best"] == "tc2")
+        # whatever the clock said: the own kernel for every bucket of the gate/up shape and the library elsewhere is a legal table
+        ops._many_choice = {(b, *gate_up_shape): "tc2" for b in ops.MANY_BUCKETS}
+        got = run_cuts(runner, "chosen", ids, [600])
+        assert rel_err(got, want) < 5e-2, rel_err(got, want)
+    finally:
+        ops._many_choice = before
+    ops.check_errors()
+
+
 def test_own_tensor_core_gemm_in_the_engine(tmp_path):
-    """Prompt steps with every many-row product on this package's two-block tcgen05 GEMM (off by default: the library's is
-    faster), the gate/up product with the activation in its epilogue: same logits as the plain implementation."""
+    """Prompt steps with every many-row product on this package's two-block tcgen05 GEMM (by default only where the start-up
+    timing finds it faster), the gate/up product with the activation in its epilogue: same logits as the plain implementation."""
     d, cfg = sized_model(tmp_path, "4b")
     ids = random_tokens(cfg["vocab_size"], 700, seed=2)
     want = plain_logits(d, ids)
