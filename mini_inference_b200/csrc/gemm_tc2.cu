@@ -27,11 +27,12 @@
 // Tiles left over after the whole waves (fewer tiles than pairs, or tiles mod pairs) are cut along K between the pairs
 // when K is long enough to pay for it: every share writes its float32 accumulator to a workspace, and once a counter
 // says that all shares of a tile are there, the shares' epilogue warps each add up and store a few [32 x 32] units of
-// it, shares in order (the same bits on every run).
+// it, shares in order (the same bits on every run).  The shares are a pair's FIRST work, so all of that happens under
+// the products of its first whole tile.
 //
 // Measured (Qwen3-4B shapes, graph-timed, microseconds own / library): 2,048 rows qkv 45.6 / 45.5, gate/up 138 / 138
-// (1.48 PFLOP/s), o 37 / 31, down 74 / 72; 4,096 rows gate/up 257 / 292-326, qkv 89 / 88; 256-1,024 rows the library
-// is 5-50 % faster.  With the activation in the epilogue the gate/up kernel replaces the library product and a 27 us
+// (1.48 PFLOP/s), o 32 / 31, down 71 / 72; 4,096 rows gate/up 257 / 292-326, qkv 89 / 88, o 60 / 60, down 139 / 140;
+// 256-1,024 rows the library is 5-50 % faster.  With the activation in the epilogue the gate/up kernel replaces the library product and a 27 us
 // activation kernel.  What made the difference (gate/up, 2,048 rows): 256-column tiles only (an MMA of 128 columns takes
 // ~150 clocks where 64 are nominal; 185 us with them), no index arithmetic between the MMAs of a stage (164), stages of
 // 128 of K (137).  The engine times both kernels per shape and row bucket at start-up and keeps the faster.
@@ -102,18 +103,26 @@ struct T2Shape {
     int full_waves, rem, split;         // tiles = full_waves * pairs + rem; each of the last rem tiles is cut along K between `split` pairs
 };
 
-// what pair `pair` does in its w-th turn: a whole tile (part < 0), or the k-steps [kc0, kc1) of one of the last tiles
+// what pair `pair` does in its w-th turn: a whole tile (part < 0), or the k-steps [kc0, kc1) of one of the left-over tiles.
+// Left-over tiles that are cut come FIRST: their shares are in the workspace, counted and added up while the first whole
+// tile's products run (the epilogue warps have nothing else to do then), so the cut costs the share's products and little
+// more.  A left-over tile that is not cut is a last, partly filled wave.
 struct T2Work { int tile, kc0, kc1, part; };
 __device__ __forceinline__ bool t2_work(const T2Shape& sh, int pair, int w, int nk, T2Work& o) {
     o.kc0 = 0; o.kc1 = nk; o.part = -1;
-    if (w < sh.full_waves) { o.tile = w * sh.pairs + pair; return true; }
-    if (w > sh.full_waves || pair >= sh.rem * sh.split) return false;
-    o.tile = sh.full_waves * sh.pairs + pair / sh.split;
-    if (sh.split > 1) {
-        o.part = pair % sh.split;
-        o.kc0 = o.part * nk / sh.split;
-        o.kc1 = (o.part + 1) * nk / sh.split;
+    if (sh.split > 1 && pair < sh.rem * sh.split) {
+        if (w == 0) {
+            o.tile = sh.full_waves * sh.pairs + pair / sh.split;
+            o.part = pair % sh.split;
+            o.kc0 = o.part * nk / sh.split;
+            o.kc1 = (o.part + 1) * nk / sh.split;
+            return true;
+        }
+        --w;
     }
+    if (w < sh.full_waves) { o.tile = w * sh.pairs + pair; return true; }
+    if (sh.split > 1 || w > sh.full_waves || pair >= sh.rem) return false;
+    o.tile = sh.full_waves * sh.pairs + pair;
     return true;
 }
 
@@ -293,6 +302,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; ++i) __stcg(dst + i * 32, __uint_as_float(ra[i]));
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_even0 + 8 * b);   // the accumulator is free for the tile after next
             __threadfence();
             __syncwarp();
             int* ctr = counters + tr * 2 + rank;
