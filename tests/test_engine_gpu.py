@@ -379,8 +379,8 @@ def test_long_prompts_under_page_pressure(tmp_path, dtype):
 
 
 def test_start_up_choice_of_many_row_kernels(tmp_path):
-    """The start-up timing of prompt-step products on the model's own weights: every shape and row bucket gets a verdict, the
-    parts' probes are used (gate/up with its activation, q/k/v with norm, rotation and cache write), only verdicts for the own
+    """The start-up timing of prompt-step products on the model's own weights: every shape and row bucket gets an answer, the
+    parts' probes are used (gate/up with its activation, q/k/v with norm, rotation and cache write), only answers for the own
     kernel are kept, and a prompt step after it still gives the plain implementation's logits."""
     d, cfg = sized_model(tmp_path, "4b")
     ids = random_tokens(cfg["vocab_size"], 600, seed=3)
