@@ -453,8 +453,11 @@ int launch_tc2(const void* X, int ldx, const void* W, void* out, int ldo, int M,
         if (split > 16) split = 16;
         const long long share = 2ll * BM * sh.BN * 4;
         while (split > 1 && (long long)sh.rem * split * share > ws_bytes) --split;
-        // a cut saves (1 - 1/split) of a tile's time (~0.7 us per 128 of K) and costs ~10 us for the pass through the workspace
-        if (split >= 2 && (long long)nk * (split - 1) >= 16ll * split) sh.split = split;
+        // a cut saves (1 - 1/split) of a tile's time (~0.7 us per 128 of K).  With whole tiles behind it, it costs the share's
+        // own products and the ring's fill (worth it from 4 saved k-steps on: gate/up at 4,096 rows 259 -> 253 us); with none,
+        // the ~10 us pass through the workspace is in the open (from 16 on)
+        const long long min_saved = sh.full_waves > 0 ? 4 : 16;
+        if (split >= 2 && (long long)nk * (split - 1) >= min_saved * split) sh.split = split;
     }
     const int pairs = sh.full_waves > 0 ? pairs_max : sh.rem * sh.split;
     sh.pairs = pairs;
