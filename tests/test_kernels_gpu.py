@@ -198,6 +198,40 @@ def test_gemm_tc2(ops, M, N, K):
     assert ops._gemm_tc(x, w, torch.float32) is None             # bfloat16 results only: the caller takes another kernel
 
 
+def test_gemm_tc2_random_shapes(ops):
+    """Shapes drawn at random: rows from 128 to 5,000, widths that are multiples of 8, depths that are multiples of 64, among them
+    many whose left-over tiles are cut along K (few tiles, long K) and many with ragged last tiles in both directions."""
+    rng = np.random.default_rng(11)
+    for case in range(24):
+        M = int(rng.integers(128, 5000)) if case % 3 else int(rng.integers(128, 700))
+        N = 8 * int(rng.integers(16, 900)) if case % 2 else 8 * int(rng.integers(16, 120))
+        K = 64 * int(rng.integers(1, 160)) if case % 4 else 64 * int(rng.integers(40, 200))
+        if M * N > 6e6:
+            N = max(128, 8 * int(6e6 / M / 8))
+        g = torch.Generator().manual_seed(case)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16).to(DEV)
+        got = ops._gemm_tc(x, w, torch.bfloat16)
+        assert got is not None, (M, N, K)
+        ops.check_errors()
+        want = x.float() @ w.float().T
+        err = ((got.float() - want).abs().max() / want.abs().max()).item()
+        assert err < 1e-2, (M, N, K, err)
+        assert int(ops._tc2_counters.abs().sum()) == 0, (M, N, K)
+        if N % 16 == 0:
+            saved = ops.tc_gemm
+            ops.tc_gemm = True
+            try:
+                act = ops.gated_linear(x, w)
+            finally:
+                ops.tc_gemm = saved
+            ops.check_errors()
+            ref = TorchRefOps()
+            want_act = ref.swiglu(ref.linear(x, w)).float()
+            err = ((act.float() - want_act).abs().max() / want_act.abs().max().clamp_min(1e-6)).item()
+            assert err < 2e-2, (M, N, K, err)
+
+
 @pytest.mark.parametrize("M,inter,K", [(512, 128, 64), (700, 264, 192), (2048, 9728, 2560), (600, 1000, 640), (513, 40, 128), (129, 64, 128),
                                        (256, 1024, 2560), (1024, 648, 512)])
 def test_gemm_tc2_swiglu(ops, M, inter, K):
