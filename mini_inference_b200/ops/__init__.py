@@ -178,7 +178,7 @@ class CudaOps:
         return y
 
     def gated_linear(self, x, w):
-        """silu(g) * u with [g | u] = x @ w.T (w = [gate rows | up rows]).  Many rows with the own tcgen05 GEMM switched on:
+        """silu(g) * u with [g | u] = x @ w.T (w = [gate rows | up rows]).  Many rows with the own tcgen05 GEMM chosen for this shape:
         one kernel whose epilogue applies the activation (csrc/gemm_tc2.cu), so the [M, 2 I] product is never written;
         otherwise product, then swiglu (or, for a few rows, the activation kernel that adds the product's partial sums)."""
         M, K = x.shape
