@@ -319,6 +319,18 @@ def test_benchmarked_decode_path(tmp_path, dtype, first_products):
         del ops.add_rmsnorm
 
 
+@pytest.mark.parametrize("case", [1, 2, 3, 5])
+def test_random_workloads_on_the_kernels(tiny_dirs, case):
+    """The randomised workloads and settings of the scheduler tests (arrivals, lengths, pools down to barely enough, budgets,
+    portions, batch limits) on the float32 kernels, with decode graphs on for half of them: tokens as the plain implementation's."""
+    from mini_inference_b200.engine.llm import LLM
+    from tests.test_scheduler_llm import random_workload
+
+    def llm(d, **kw):
+        return LLM(d, dtype="float32", device=DEV, cuda_graphs=case % 2 == 1, **kw)
+    random_workload(tiny_dirs, case, llm)
+
+
 def test_scheduler_in_bfloat16_is_judged_by_logits(tiny_dirs):
     """Chunked prompts, CUDA graphs, overlapped decode and a pool small enough to preempt, in bfloat16: every generated
     token is judged at its own position against the plain implementation (the logits of prompt + generated, and the token

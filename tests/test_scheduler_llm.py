@@ -179,6 +179,49 @@ def test_arrivals_mid_run_and_temperature(tiny_dirs):
         assert sc[alone[2][k]] >= sc.max() - 1e-3
 
 
+@pytest.mark.parametrize("case", range(6))
+def test_random_workloads_and_settings(tiny_dirs, case):
+    """Workloads and engine settings drawn at random (arrival steps, prompt and output lengths, page pools from roomy to
+    barely enough for the longest request, step budgets, portions on or off, batch limits): every request's greedy tokens are
+    the plain implementation's, the cache manager's invariants hold after every step, and all pages come back."""
+    random_workload(tiny_dirs, case, llm)
+
+
+def random_workload(tiny_dirs, case, llm):
+    import numpy as np
+    rng = np.random.default_rng(100 + case)
+    name = ("A", "B", "W")[case % 3]
+    d, cfg, page = tiny_dirs[name]
+    c, w = plain.load_model_dir(d)
+    n = int(rng.integers(3, 8))
+    lens = [int(rng.integers(1, 40)) for _ in range(n)]
+    news = [int(rng.integers(1, 14)) for _ in range(n)]
+    arrive = sorted(int(rng.integers(0, 12)) for _ in range(n))
+    prompts = [random_tokens(cfg["vocab_size"], L, seed=500 + 10 * case + i) for i, L in enumerate(lens)]
+    want = [plain.greedy_generate(c, w, p, k) for p, k in zip(prompts, news)]
+    longest = max(L + k for L, k in zip(lens, news))
+    pages_longest = -(-longest // page)
+    pool_pages = int(rng.integers(pages_longest + 1, 4 * pages_longest + 2))
+    chunked = bool(rng.integers(0, 2))
+    budget = int(rng.integers(2, 24)) if chunked else int(rng.integers(max(lens), 3 * max(lens) + 1))
+    eng = llm(d, kv_block_size=page, kv_cache_tokens=pool_pages * page, kv_watermark=0.0, chunked_prefill=chunked,
+              max_batched_tokens=budget, max_num_seqs=int(rng.integers(1, 5)))
+    total_pages = eng.cache.free_pages()
+    reqs, step = [None] * n, 0
+    while any(r is None for r in reqs) or eng.has_work():
+        for i in range(n):
+            if reqs[i] is None and arrive[i] <= step:
+                reqs[i] = eng.add_request(prompts[i], SamplingParams(max_new_tokens=news[i]))
+        eng.step()
+        eng.cache.check_invariants()
+        step += 1
+        assert step < 3000, "the engine does not finish"
+    setting = dict(config=name, pool_pages=pool_pages, chunked=chunked, budget=budget, lens=lens, news=news, arrive=arrive)
+    assert [r.output_ids for r in reqs] == want, setting
+    assert all(r.error is None for r in reqs), setting
+    assert eng.cache.free_pages() == total_pages and eng.stats()["running"] == 0, setting
+
+
 def test_limits_and_errors(tiny_dirs):
     d, cfg, page = tiny_dirs["A"]
     eng = llm(d, kv_block_size=8, kv_cache_tokens=64)
